@@ -81,3 +81,41 @@ extern "C" int rv_xielu_act(const void* in, const float* act, void* out, int dty
     RV_CHECK_LAUNCH("xielu");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------
+// The clamped gated activation of a feed-forward whose gate and up rows come out of one product
+// as [N, 2F] (gate values, then up values), with an optional bias [2F] added first:
+//   g = min(gate, limit);  u = clamp(up, -limit, limit);  out = g * sigmoid(alpha g) * (u + 1)
+// Arithmetic in float32.  Plain reference: tests/plain_ops.py glu_clamp.
+template <typename T>
+__global__ void glu_clamp_kernel(const T* __restrict__ in, const float* __restrict__ bias,
+                                 T* __restrict__ out, size_t total, int F, float limit,
+                                 float alpha) {
+    rv_pdl_prologue();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / F;
+        const int f = (int)(i - row * F);
+        float g = rv_load(in + row * 2 * F + f), u = rv_load(in + row * 2 * F + F + f);
+        if (bias) {
+            g += bias[f];
+            u += bias[F + f];
+        }
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        rv_store(out + i, g / (1.f + expf(-alpha * g)) * (u + 1.f));
+    }
+}
+
+extern "C" int rv_glu_clamp(const void* in, const float* bias, void* out, int dtype, int n_rows,
+                            int F, float limit, float alpha, void* stream) {
+    if (n_rows == 0) return 0;
+    if (n_rows < 0 || F <= 0) RV_FAIL("glu_clamp: bad sizes");
+    const size_t total = (size_t)n_rows * F;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    RV_DISPATCH_DTYPE(dtype, "glu_clamp",
+                      (rv_launch(glu_clamp_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
+                                 (const T*)in, bias, (T*)out, total, F, limit, alpha)));
+    RV_CHECK_LAUNCH("glu_clamp");
+    return 0;
+}

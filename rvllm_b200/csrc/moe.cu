@@ -8,13 +8,18 @@
 //                  s, and only experts of the `keep` best groups can be chosen; the `top`
 //                  largest allowed s are chosen (ties: the lower index first, for groups too);
 //                  weights = chosen s / (their sum + weight_eps).  One warp per token.
+//                  Options: score_mode 1 makes s the softmax of the logits over all experts
+//                  instead of their sigmoids; renorm 0 leaves the chosen s undivided; every
+//                  weight is multiplied by route_scale.
 //   moe_route      the router's product (x [N, W] of any type, router float32 [E, W]) and the same
 //                  choice in one kernel.
 //   moe_gate_up    act[pair, f] = silu(<gate_e[f], x_t>) * <up_e[f], x_t> for pair = t * top + k,
 //                  e = ids[t, k]; gate_up is [E, 2F, W] with gate and up rows alternating
-//                  (row 2f: gate f, row 2f + 1: up f).
+//                  (row 2f: gate f, row 2f + 1: up f).  act_mode 1: with g = min(gate, limit) and
+//                  u = clamp(up, -limit, limit) the value is g * sigmoid(alpha g) * (u + 1).
 //   moe_down       out[t, w] = sum_k weights[t, k] * <down_e(k)[w], act[t * top + k]>, the sum in
-//                  the order of k; down is [E, W, F].
+//                  the order of k; down is [E, W, F].  `addend` [N, W], if given, is where each sum
+//                  starts (the output of an expert that every token uses).
 // Dot products and the activation are float32; act is rounded to the storage type.
 // Plain references: tests/plain_ops.py moe_select, moe_experts.
 #include "common.cuh"
@@ -50,8 +55,23 @@ __device__ __forceinline__ void moe_warp_argmax(const float* sc, int lo, int hi,
 __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int top, int groups,
                                                 int keep, int group_top, float weight_eps,
                                                 int* __restrict__ ids, float* __restrict__ weights,
-                                                int lane) {
-    for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
+                                                int lane, int score_mode = 0, int renorm = 1,
+                                                float route_scale = 1.f) {
+    if (score_mode == 1) {                           // softmax over all experts
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
+        m = rv_warp_max(m);
+        float tot = 0.f;
+        for (int e = lane; e < E; e += 32) {
+            const float v = expf(sc[e] - m);
+            sc[e] = v;
+            tot += v;
+        }
+        tot = rv_warp_sum(tot);
+        for (int e = lane; e < E; e += 32) sc[e] = sc[e] / tot;
+    } else {
+        for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
+    }
     __syncwarp();
     if (groups > 1) {
         const int size = E / groups;
@@ -124,7 +144,7 @@ __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int
         if (lane == 0) sc[i] = -2.f;
         __syncwarp();
     }
-    const float inv = 1.f / (sum + weight_eps);
+    const float inv = (renorm ? 1.f / (sum + weight_eps) : 1.f) * route_scale;
     if (lane < top) {
         ids[lane] = mine_id;
         weights[lane] = mine * inv;
@@ -135,7 +155,8 @@ __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int
 
 __global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
                                   int groups, int keep, int group_top, float weight_eps,
-                                  int* __restrict__ ids, float* __restrict__ weights) {
+                                  int* __restrict__ ids, float* __restrict__ weights, int score_mode,
+                                  int renorm, float route_scale) {
     rv_pdl_prologue();
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
@@ -145,7 +166,8 @@ __global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens
     for (int e = lane; e < E; e += 32) sc[e] = logits[(size_t)t * E + e];
     __syncwarp();
     moe_select_warp(sc, sc + E, E, top, groups, keep, group_top, weight_eps,
-                    ids + (size_t)t * top, weights + (size_t)t * top, lane);
+                    ids + (size_t)t * top, weights + (size_t)t * top, lane, score_mode, renorm,
+                    route_scale);
 }
 
 // The router's product and the choice in one kernel: a block takes MOE_ROUTE_TOK tokens; each
@@ -172,7 +194,7 @@ template <typename T>
 __global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
     const T* __restrict__ x, const float* __restrict__ router, int n_tokens, int W, int E, int top,
     int groups, int keep, int group_top, float weight_eps, int* __restrict__ ids,
-    float* __restrict__ weights, int stage_rows) {
+    float* __restrict__ weights, int stage_rows, int score_mode, int renorm, float route_scale) {
     rv_pdl_prologue();
     extern __shared__ __align__(16) float smem[];        // [MOE_ROUTE_TOK][E + groups], then the rows
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -237,7 +259,7 @@ __global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
         int* my_ids = ids + (size_t)(t0 + warp) * top;
         float* my_weights = weights + (size_t)(t0 + warp) * top;
         moe_select_warp(sc, sc + E, E, top, groups, keep, group_top, weight_eps, my_ids, my_weights,
-                        lane);
+                        lane, score_mode, renorm, route_scale);
     }
 }
 
@@ -247,7 +269,7 @@ __global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
 template <typename T>
 __global__ void moe_gate_up_kernel(const T* __restrict__ x, const int* __restrict__ ids,
                                    const T* __restrict__ gate_up, T* __restrict__ act, int top,
-                                   int E, int W, int F) {
+                                   int E, int W, int F, int act_mode, float limit, float alpha) {
     rv_pdl_prologue();
     extern __shared__ float xs[];                      // [W]
     const int pair = blockIdx.x;
@@ -270,14 +292,25 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ x, const int* __restric
         }
         g = rv_warp_sum(g);
         u = rv_warp_sum(u);
-        if (lane == 0) rv_store(act + (size_t)pair * F + f, g / (1.f + expf(-g)) * u);
+        if (lane == 0) {
+            float v;
+            if (act_mode == 1) {
+                g = fminf(g, limit);
+                u = fminf(fmaxf(u, -limit), limit);
+                v = g / (1.f + expf(-alpha * g)) * (u + 1.f);
+            } else {
+                v = g / (1.f + expf(-g)) * u;
+            }
+            rv_store(act + (size_t)pair * F + f, v);
+        }
     }
 }
 
 template <typename T>
 __global__ void moe_down_kernel(const T* __restrict__ act, const int* __restrict__ ids,
                                 const float* __restrict__ weights, const T* __restrict__ down,
-                                T* __restrict__ out, int top, int E, int W, int F) {
+                                const T* __restrict__ addend, T* __restrict__ out, int top, int E,
+                                int W, int F) {
     rv_pdl_prologue();
     extern __shared__ float as[];                      // [top * F]
     const int t = blockIdx.x;
@@ -287,7 +320,7 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const int* __restrict
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int w_end = min(W, (int)(blockIdx.y + 1) * MOE_ROWS);
     for (int w = blockIdx.y * MOE_ROWS + warp; w < w_end; w += nwarps) {
-        float y = 0.f;
+        float y = addend ? rv_load(addend + (size_t)t * W + w) : 0.f;
         for (int k = 0; k < top; ++k) {
             const int e = ids[(size_t)t * top + k];
             if (e < 0 || e >= E) continue;
@@ -303,7 +336,7 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const int* __restrict
 
 extern "C" int rv_moe_select(const float* logits, int n_tokens, int E, int top, int groups,
                              int keep, int group_top, float weight_eps, int* ids, float* weights,
-                             void* stream) {
+                             int score_mode, int renorm, float route_scale, void* stream) {
     if (n_tokens == 0) return 0;
     if (n_tokens < 0 || E < 1 || top < 1 || top > E) RV_FAIL("moe_select: bad sizes");
     if (groups < 1 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < top)
@@ -316,14 +349,15 @@ extern "C" int rv_moe_select(const float* logits, int n_tokens, int E, int top, 
     if (smem > 48 * 1024) RV_FAIL("moe_select: too many experts");
     rv_launch(moe_select_kernel, dim3((n_tokens + wpb - 1) / wpb), dim3(wpb * 32), smem,
               (cudaStream_t)stream, logits, n_tokens, E, top, groups, keep, group_top, weight_eps,
-              ids, weights);
+              ids, weights, score_mode, renorm, route_scale);
     RV_CHECK_LAUNCH("moe_select");
     return 0;
 }
 
 extern "C" int rv_moe_route(const void* x, int dtype, const float* router, int n_tokens, int W,
                             int E, int top, int groups, int keep, int group_top, float weight_eps,
-                            int* ids, float* weights, void* stream) {
+                            int* ids, float* weights, int score_mode, int renorm, float route_scale,
+                            void* stream) {
     if (n_tokens == 0) return 0;
     if (n_tokens < 0 || W < 1 || E < 1 || top < 1 || top > E) RV_FAIL("moe_route: bad sizes");
     if (groups < 1 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < top)
@@ -341,7 +375,8 @@ extern "C" int rv_moe_route(const void* x, int dtype, const float* router, int n
     RV_DISPATCH_DTYPE(dtype, "moe_route",
                       (rv_launch(moe_route_kernel<T>, dim3(blocks), dim3(MOE_ROUTE_TOK * 32), smem,
                                  (cudaStream_t)stream, (const T*)x, router, n_tokens, W, E, top,
-                                 groups, keep, group_top, weight_eps, ids, weights, stage_rows)));
+                                 groups, keep, group_top, weight_eps, ids, weights, stage_rows,
+                                 score_mode, renorm, route_scale)));
     RV_CHECK_LAUNCH("moe_route");
     return 0;
 }
@@ -349,7 +384,8 @@ extern "C" int rv_moe_route(const void* x, int dtype, const float* router, int n
 // act: scratch [n_tokens * top, F] of the storage type.
 extern "C" int rv_moe_experts_simple(const void* x, int dtype, const int* ids, const float* weights,
                                      const void* gate_up, const void* down, void* act, void* out,
-                                     int n_tokens, int top, int E, int W, int F, void* stream) {
+                                     int n_tokens, int top, int E, int W, int F, int act_mode,
+                                     float limit, float alpha, const void* addend, void* stream) {
     if (n_tokens == 0) return 0;
     if (n_tokens < 0 || top < 1 || E < 1 || W < 1 || F < 1) RV_FAIL("moe_experts: bad sizes");
     if ((size_t)W * 4 > 200 * 1024 || (size_t)top * F * 4 > 200 * 1024)
@@ -365,9 +401,11 @@ extern "C" int rv_moe_experts_simple(const void* x, int dtype, const int* ids, c
             cudaFuncSetAttribute(moe_down_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)smem2);
         rv_launch(moe_gate_up_kernel<T>, dim3(n_tokens * top, (F + MOE_ROWS - 1) / MOE_ROWS),
-                  dim3(128), smem1, s, (const T*)x, ids, (const T*)gate_up, (T*)act, top, E, W, F);
+                  dim3(128), smem1, s, (const T*)x, ids, (const T*)gate_up, (T*)act, top, E, W, F,
+                  act_mode, limit, alpha);
         rv_launch(moe_down_kernel<T>, dim3(n_tokens, (W + MOE_ROWS - 1) / MOE_ROWS), dim3(128),
-                  smem2, s, (const T*)act, ids, weights, (const T*)down, (T*)out, top, E, W, F);
+                  smem2, s, (const T*)act, ids, weights, (const T*)down, (const T*)addend, (T*)out, top,
+                  E, W, F);
     });
     RV_CHECK_LAUNCH("moe_experts");
     return 0;

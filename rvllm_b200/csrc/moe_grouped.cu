@@ -95,14 +95,24 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ x, const int* __restr
 
 // one block per token; width a multiple of 8
 __global__ void moe_combine_kernel(const bf16* __restrict__ ys, const int* __restrict__ pair_pos,
-                                   const float* __restrict__ weights, bf16* __restrict__ out, int top,
-                                   int W) {
+                                   const float* __restrict__ weights, const bf16* __restrict__ addend,
+                                   bf16* __restrict__ out, int top, int W) {
     rv_pdl_prologue();
     const int t = blockIdx.x;
     for (int i = threadIdx.x; i < W / 8; i += blockDim.x) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        if (addend) {                                  // rows that every token gets (a shared expert)
+            const uint4 raw = *((const uint4*)(addend + (size_t)t * W) + i);
+            const __nv_bfloat162* h = (const __nv_bfloat162*)&raw;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h[j]);
+                acc[2 * j] = f.x;
+                acc[2 * j + 1] = f.y;
+            }
+        }
         for (int k = 0; k < top; ++k) {
             const float wgt = weights[(size_t)t * top + k];
             const uint4 raw = *((const uint4*)(ys + (size_t)pair_pos[(size_t)t * top + k] * W) + i);
@@ -126,12 +136,16 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ ys, const int* __res
 // 128 rows of W a block multiplies with its token tile; with two, the tokens' tile is copied
 // once for twice the products (the kernel is bound by what an SM copies from L2: 32 KB per 64
 // of K with one tile, 48 KB for two), each with an accumulator of its own in TMEM.
-template <bool SWIGLU>
+// ACT: 0 = the sums as they are; 1 = silu(gate) * up; 2 = the clamped form
+//   g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(alpha g) * (u + 1)
+// of pairs of neighbouring rows of W.
+template <int ACT>
 __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     bf16* __restrict__ out, int* __restrict__ status, const int* __restrict__ tile_expert,
     const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, int n_out, int kblocks,
-    int TN, int stages, int MT) {
+    int TN, int stages, int MT, float limit, float alpha) {
+    constexpr bool SWIGLU = ACT != 0;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int w_half = MG_BM * MG_BK * 2;                     // one tile of 128 rows of W
@@ -264,8 +278,15 @@ __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
                     const float got = __shfl_xor_sync(0xffffffffu, odd ? mine0 : mine1, 1);
                     const float g = odd ? got : mine0;         // odd: the gate of token j + 1
                     const float u = odd ? mine1 : got;         // even: the up value of token j
+                    float res;
+                    if (ACT == 2) {
+                        const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
+                        res = __fdividef(gc, 1.f + __expf(-alpha * gc)) * (uc + 1.f);
+                    } else {
+                        res = __fdividef(g, 1.f + __expf(-g)) * u;
+                    }
                     stage_out[(c + j + (odd ? 1 : 0)) * SW + (n_local >> 1)] =
-                        __float2bfloat16_rn(__fdividef(g, 1.f + __expf(-g)) * u);
+                        __float2bfloat16_rn(res);
                 }
             } else {
 #pragma unroll
@@ -297,10 +318,13 @@ extern "C" long long rv_moe_grouped_rows(int pairs, int E, int TN) {
 }
 
 extern "C" int rv_moe_grouped_init() {
-    cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<true>,
+    cudaError_t e = cudaFuncSetAttribute(moe_grouped_kernel<0>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_MAX);
     if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(moe_grouped_kernel<false>,
+        e = cudaFuncSetAttribute(moe_grouped_kernel<1>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_MAX);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(moe_grouped_kernel<2>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_MAX);
     if (e != cudaSuccess) RV_FAIL("moe_grouped: %s", cudaGetErrorString(e));
     if (!encode_fn()) RV_FAIL("moe_grouped: cuTensorMapEncodeTiled is not available in this driver");
@@ -309,7 +333,8 @@ extern "C" int rv_moe_grouped_init() {
 
 static int grouped_product(const void* xs, const void* w, void* out, int* status, const int* tile_expert,
                            const int* tile_row0, const int* n_tiles, long long rows, int E, int n_out,
-                           int K, int TN, int max_tiles, bool swiglu, cudaStream_t stream) {
+                           int K, int TN, int max_tiles, int act, float limit, float alpha,
+                           cudaStream_t stream) {
     CUtensorMap map_w, map_x;
     if (make_map(&map_w, w, (long long)E * n_out, K, MG_BM)) return 1;
     if (make_map(&map_x, xs, rows, K, TN)) return 1;
@@ -326,12 +351,15 @@ static int grouped_product(const void* xs, const void* w, void* out, int* status
     if (stages < 2) stages = 2;
     const size_t smem = (size_t)stages * per_stage + 1024;
     dim3 grid((n_out + MT * MG_BM - 1) / (MT * MG_BM), max_tiles);
-    if (swiglu)
-        rv_launch(moe_grouped_kernel<true>, grid, dim3(128), smem, stream, map_w, map_x, (bf16*)out,
-                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages, MT);
+    if (act == 2)
+        rv_launch(moe_grouped_kernel<2>, grid, dim3(128), smem, stream, map_w, map_x, (bf16*)out,
+                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages, MT, limit, alpha);
+    else if (act == 1)
+        rv_launch(moe_grouped_kernel<1>, grid, dim3(128), smem, stream, map_w, map_x, (bf16*)out,
+                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages, MT, limit, alpha);
     else
-        rv_launch(moe_grouped_kernel<false>, grid, dim3(128), smem, stream, map_w, map_x, (bf16*)out,
-                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages, MT);
+        rv_launch(moe_grouped_kernel<0>, grid, dim3(128), smem, stream, map_w, map_x, (bf16*)out,
+                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages, MT, limit, alpha);
     RV_CHECK_LAUNCH("moe_grouped");
     return 0;
 }
@@ -349,11 +377,14 @@ extern "C" int rv_moe_experts_grouped(const void* x, const int* ids, const float
                                       const void* gate_up, const void* down, void* out,
                                       void* scratch, long long scratch_bytes, int* status,
                                       int n_tokens, int top, int E, int W, int F, int TN,
+                                      int act_mode, float limit, float alpha, const void* addend,
                                       void* stream) {
     if (n_tokens == 0) return 0;
     if (n_tokens < 0 || top < 1 || E < 1 || W < 8 || F < 8 || W % 8 || F % 8)
         RV_FAIL("moe_experts_grouped: widths must be multiples of 8");
     if (TN != 16 && TN != 32 && TN != 64 && TN != 128) RV_FAIL("moe_experts_grouped: bad token tile");
+    if (act_mode != 0 && act_mode != 1) RV_FAIL("moe_experts_grouped: unknown activation %d", act_mode);
+    if ((uintptr_t)addend & 15) RV_FAIL("moe_experts_grouped: the added rows must be 16-byte aligned");
     if ((size_t)3 * E * sizeof(int) > 48 * 1024) RV_FAIL("moe_experts_grouped: too many experts");
     const long long pairs = (long long)n_tokens * top;
     if (pairs > 0x3fffffffLL) RV_FAIL("moe_experts_grouped: too many rows");
@@ -381,13 +412,14 @@ extern "C" int rv_moe_experts_grouped(const void* x, const int* ids, const float
               (const int*)sorted_token, xs, (int)rows, W);
     RV_CHECK_LAUNCH("moe_gather");
     if (grouped_product(xs, gate_up, act, status, tile_expert, tile_row0, n_tiles, rows, E, 2 * F, W,
-                        TN, max_tiles, true, s))
+                        TN, max_tiles, act_mode == 1 ? 2 : 1, limit, alpha, s))
         return 1;
     if (grouped_product(act, down, ys, status, tile_expert, tile_row0, n_tiles, rows, E, W, F, TN,
-                        max_tiles, false, s))
+                        max_tiles, 0, 0.f, 0.f, s))
         return 1;
     rv_launch(moe_combine_kernel, dim3(n_tokens), dim3(W / 8 < 256 ? ((W / 8 + 31) / 32) * 32 : 256), 0,
-              s, (const bf16*)ys, (const int*)pair_pos, weights, (bf16*)out, top, W);
+              s, (const bf16*)ys, (const int*)pair_pos, weights, (const bf16*)addend, (bf16*)out, top,
+              W);
     RV_CHECK_LAUNCH("moe_combine");
     return 0;
 }

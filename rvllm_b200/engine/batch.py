@@ -62,6 +62,8 @@ class StepContext:
     max_q_len: int = 0
     max_ctx_len: int = 0
     n_wanted: int = 0               # logit rows that were asked for (the first ones)
+    # what one call of the run order leaves for later calls of the same step (by name)
+    carry: dict = field(default_factory=dict)
 
 
 def _align(n: int) -> int:

@@ -10,7 +10,7 @@ import torch
 from ..cache import CacheManager
 from ..config.registry import architecture, load_config
 from ..parts.model import Model
-from ..weights.loader import load_tensors
+from ..weights.loader import load_tensors, tensor_shapes
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
           "float32": torch.float32, "fp32": torch.float32}
@@ -31,6 +31,10 @@ def load_model(folder: str, dtype="bfloat16", device="cuda", ops=None):
     import fails loudly when the native library cannot be built or loaded."""
     dtype = parse_dtype(dtype)
     config = load_config(folder)
+    complete = getattr(config, "with_tensor_shapes", None)
+    if complete is not None:
+        # sizes that no key names are taken from the tensor file's header
+        config = complete(tensor_shapes(folder))
     spec = architecture(config.architecture).build_spec(config)
     if ops is None:
         from ..kernels import cuda_ops

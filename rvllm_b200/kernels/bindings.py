@@ -936,7 +936,14 @@ class CudaOps:
 
     # ---- mixture of experts ---------------------------------------------------------------
 
-    def moe_select(self, logits, groups, keep, group_top, weight_eps, ids, weights):
+    SCORE_MODES = {"sigmoid": 0, "softmax": 1}
+    EXPERT_ACTIVATIONS = {"swiglu": 0, "glu_clamp": 1}
+
+    def moe_select(self, logits, groups, keep, group_top, weight_eps, ids, weights,
+                   score="sigmoid", renormalize=True, route_scale=1.0):
+        """`score`: how logits become scores ("sigmoid", or "softmax" over all experts);
+        `renormalize` false: the chosen scores are not divided by their sum; every weight is
+        multiplied by `route_scale`."""
         self._need(logits, "router logits", torch.float32)
         self._need(ids, "expert ids", torch.int32)
         self._need(weights, "expert weights", torch.float32)
@@ -944,9 +951,11 @@ class CudaOps:
         self._check(self.lib.rv_moe_select(
             _ptr(logits), c_int(n), c_int(experts), c_int(ids.shape[1]), c_int(groups),
             c_int(keep), c_int(group_top), c_float(weight_eps), _ptr(ids), _ptr(weights),
+            c_int(self.SCORE_MODES[score]), c_int(1 if renormalize else 0), c_float(route_scale),
             self._stream()), "moe_select")
 
-    def moe_route(self, x, router, groups, keep, group_top, weight_eps, ids, weights):
+    def moe_route(self, x, router, groups, keep, group_top, weight_eps, ids, weights,
+                  score="sigmoid", renormalize=True, route_scale=1.0):
         """The router's product (float32 `router` [experts, width], float32 sums) and the
         choice of `moe_select`, in one kernel."""
         self._need(x, "feed-forward input")
@@ -959,11 +968,20 @@ class CudaOps:
         self._check(self.lib.rv_moe_route(
             _ptr(x), _code(x.dtype), _ptr(router), c_int(x.shape[0]), c_int(width), c_int(experts),
             c_int(ids.shape[1]), c_int(groups), c_int(keep), c_int(group_top), c_float(weight_eps),
-            _ptr(ids), _ptr(weights), self._stream()), "moe_route")
+            _ptr(ids), _ptr(weights), c_int(self.SCORE_MODES[score]),
+            c_int(1 if renormalize else 0), c_float(route_scale), self._stream()), "moe_route")
 
-    def moe_experts(self, x, ids, weights, gate_up, down, out):
-        """out[t] = sum_k weights[t, k] * down[e](silu(gate[e] x_t) * up[e] x_t), e = ids[t, k];
-        gate_up [E, 2F, W] (gate rows, then up rows), down [E, W, F]."""
+    def moe_experts(self, x, ids, weights, gate_up, down, out, activation="swiglu", limit=0.0,
+                    alpha=1.0, addend=None):
+        """out[t] = sum_k weights[t, k] * down[e](act(gate[e] x_t, up[e] x_t)), e = ids[t, k];
+        gate_up [E, 2F, W] (gate and up rows alternating), down [E, W, F].  `activation`
+        "swiglu": silu(gate) * up; "glu_clamp": g = min(gate, limit), u = clamp(up, -limit,
+        limit), g * sigmoid(alpha g) * (u + 1).  `addend` [N, W]: rows each sum starts from."""
+        act_mode = self.EXPERT_ACTIVATIONS[activation]
+        if addend is not None:
+            self._need(addend, "rows added to the experts' output", x.dtype)
+            if addend.shape != out.shape:
+                raise KernelError("moe_experts: the added rows and the output differ in shape")
         self._need(x, "feed-forward input")
         self._need(gate_up, "experts' gate and up matrices", x.dtype)
         self._need(down, "experts' down matrices", x.dtype)
@@ -985,7 +1003,8 @@ class CudaOps:
             self._check(self.lib.rv_moe_experts_grouped(
                 _ptr(x), _ptr(ids), _ptr(weights), _ptr(gate_up), _ptr(down), _ptr(out),
                 _ptr(scratch), c_longlong(need), _ptr(self._gemm_status(x.device)), c_int(n),
-                c_int(top), c_int(experts), c_int(width), c_int(ffn), c_int(tn), self._stream()),
+                c_int(top), c_int(experts), c_int(width), c_int(ffn), c_int(tn), c_int(act_mode),
+                c_float(limit), c_float(alpha), _ptr(addend), self._stream()),
                 "moe_experts_grouped")
             self.launches += 4
             return
@@ -993,8 +1012,116 @@ class CudaOps:
         self._check(self.lib.rv_moe_experts_simple(
             _ptr(x), _code(x.dtype), _ptr(ids), _ptr(weights), _ptr(gate_up), _ptr(down),
             _ptr(act), _ptr(out), c_int(n), c_int(top), c_int(experts), c_int(width), c_int(ffn),
-            self._stream()), "moe_experts")
+            c_int(act_mode), c_float(limit), c_float(alpha), _ptr(addend), self._stream()),
+            "moe_experts")
         self.launches += 1
+
+    # ---- hyper-connections -----------------------------------------------------------------
+
+    def hyper_norm(self, src, dst, delta, mix, out_w, in_w, weight, eps, out, rows=None):
+        """The step between two sub-layers of a block with several residual streams:
+        x'_t = sum_s mix[s, t] x_s + out_w[t] delta (skipped without `delta`), written to `dst`
+        [N, S, W] when given; u = sum_t in_w[t] x'_t (`in_w` None: the plain sum); `out` =
+        RMSNorm(u) with `weight`.  `src` is [N, S, W] or, before the streams differ, [N, W].
+        With `rows` only those rows are read and nothing is written back."""
+        self._need(src, "residual streams", torch.float32)
+        self._need(weight, "norm weight", torch.float32)
+        self._need(out, "norm output")
+        n_out, width = out.shape
+        if dst is not None:
+            self._need(dst, "residual streams", torch.float32)
+            streams = dst.shape[1]
+        else:
+            streams = src.shape[1] if src.dim() == 3 else (in_w.shape[0] if in_w is not None else 1)
+        for t, what in ((mix, "mixing matrix"), (out_w, "output weights"), (in_w, "input weights")):
+            if t is not None:
+                self._need(t, what, torch.float32)
+        if delta is not None:
+            self._need(delta, "pending sub-layer output")
+        if rows is not None:
+            self._need(rows, "row list", torch.int32)
+        if src.shape[-1] != width or weight.shape[0] != width:
+            raise KernelError("hyper_norm: widths disagree")
+        self._check(self.lib.rv_hyper_norm(
+            _ptr(src), c_int(streams if src.dim() == 3 else 1), _ptr(dst), _ptr(delta),
+            _code(delta.dtype) if delta is not None else _F32, _ptr(mix), _ptr(out_w), _ptr(in_w),
+            _ptr(weight), _ptr(out), _code(out.dtype), _ptr(rows), c_int(n_out), c_int(streams),
+            c_int(width), c_float(eps), self._stream()), "hyper_norm")
+
+    # ---- whole-projection q/k norm + pairwise rotation + value mixing + cache write --------
+
+    def qkv_full_norm_rope_write(self, rows, bias, num_heads, num_kv_heads, head_dim, v_head_dim,
+                                 q_weight, k_weight, eps, freq, rot_dims, positions, slot_mapping,
+                                 q_out, k_cache, v_cache, v_first_in=None, v_first_out=None,
+                                 lam=None):
+        """`rows` float32 [N, (heads + kv) * head_dim + kv * v_head_dim] (+ `bias`): q and k are
+        normalised over their whole projection (weights [heads * head_dim], [kv * head_dim]),
+        the pairs (2i, 2i + 1) of each head's first `rot_dims` dimensions turn by position *
+        freq[i]; v <- (1 - lam) v + lam v_first_in when given (`lam` a float32 scalar tensor);
+        `v_first_out` receives this layer's own values.  q -> `q_out`, k and v -> the cache."""
+        self._need(rows, "q|k|v rows", torch.float32)
+        self._need(q_out, "query rows", k_cache.dtype)
+        for t, what in ((bias, "bias"), (q_weight, "query norm weight"), (k_weight, "key norm weight"),
+                        (freq, "rotation frequencies"), (v_first_in, "first values"),
+                        (v_first_out, "first values"), (lam, "mixing weight")):
+            if t is not None:
+                self._need(t, what, torch.float32)
+        total = (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_head_dim
+        if rows.shape[1] != total or q_out.shape[1] != num_heads * head_dim:
+            raise KernelError("qkv_full_norm_rope_write: row width and head sizes disagree")
+        self._check(self.lib.rv_qkv_full_norm_rope_write(
+            _ptr(rows), _ptr(bias), _ptr(q_weight), _ptr(k_weight), c_float(eps), _ptr(freq),
+            c_int(rot_dims), _ptr(positions), _ptr(slot_mapping), _ptr(q_out), _ptr(k_cache),
+            _ptr(v_cache), _code(k_cache.dtype), _ptr(v_first_in), _ptr(v_first_out), _ptr(lam),
+            c_int(rows.shape[0]), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+            c_int(v_head_dim), self._stream()), "qkv_full_norm_rope_write")
+
+    # ---- gated delta rule ------------------------------------------------------------------
+
+    def gated_delta_record(self, heads, kv_heads, dim, vdim, taps) -> int:
+        """Floats of one request's record: convolution inputs, then the state."""
+        return (taps - 1) * (2 * kv_heads * dim + heads * vdim) + heads * dim * vdim
+
+    def gated_delta(self, proj, lowrank, filt, a_log, dt_bias, norm_w, state, ctx, out, heads,
+                    kv_heads, dim, vdim, taps, unit_eps, eps):
+        """The gated delta rule with a decay per key channel over the step's tokens; see
+        csrc/gated_delta.cu for the layout of `proj`, `lowrank` and the record."""
+        for t, what in ((proj, "projection rows"), (lowrank, "decay and gate rows"),
+                        (filt, "convolution filters"), (a_log, "decay rates"),
+                        (dt_bias, "decay bias"), (norm_w, "output norm weight"),
+                        (state, "state records")):
+            self._need(t, what, torch.float32)
+        self._need(out, "mixer output")
+        rec = self.gated_delta_record(heads, kv_heads, dim, vdim, taps)
+        if state.shape[1] != rec or out.shape[1] != heads * vdim:
+            raise KernelError("gated_delta: the record or the output has another size")
+        n = proj.shape[0]
+        channels = 2 * kv_heads * dim + heads * vdim
+        prep = torch.empty((n, channels + heads + heads * dim), dtype=torch.float32,
+                           device=proj.device)
+        self._check(self.lib.rv_gated_delta(
+            _ptr(proj), c_int(proj.shape[1]), _ptr(lowrank), c_int(lowrank.shape[1]), _ptr(filt),
+            _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), _ptr(state), _ptr(ctx.token_req),
+            _ptr(ctx.q_start), _ptr(ctx.state_slot), _ptr(prep), _ptr(out), _code(out.dtype),
+            c_int(n), c_int(ctx.n_reqs), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim),
+            c_int(taps), c_float(unit_eps), c_float(eps), self._stream()), "gated_delta")
+        self.launches += 1
+
+    # ---- clamped gated activation ----------------------------------------------------------
+
+    def glu_clamp(self, gate_up, bias, out, limit, alpha):
+        """out = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, +-limit);
+        `gate_up` [N, 2F] holds gate values then up values, `bias` float32 [2F] is added first."""
+        self._need(gate_up, "gate|up rows")
+        self._need(out, "activation output", gate_up.dtype)
+        if bias is not None:
+            self._need(bias, "bias", torch.float32)
+        n, f = out.shape
+        if gate_up.shape != (n, 2 * f):
+            raise KernelError("glu_clamp: shapes disagree")
+        self._check(self.lib.rv_glu_clamp(_ptr(gate_up), _ptr(bias), _ptr(out), _code(out.dtype),
+                                          c_int(n), c_int(f), c_float(limit), c_float(alpha),
+                                          self._stream()), "glu_clamp")
 
     def softcap(self, logits, cap):
         self._need(logits, "logits", torch.float32)

@@ -1,8 +1,8 @@
 """Parts a model is put together from: mixers, feed-forwards, norms, position
 encodings and their arrangement in a block.  Importing the package registers the
 built-in kinds."""
-from . import (attention, attention_latent, attention_mixed, block, feed_forward, mingru, norm,  # noqa: F401
-               position, short_conv)
+from . import (attention, attention_latent, attention_mixed, block, feed_forward, gated_delta,  # noqa: F401
+               hyper, mingru, norm, position, short_conv)
 from .base import (Arrangement, FeedForward, Mixer, Norm, PagedNeed, PositionEncoding,
                    StateNeed, Stream, arrangement_class, feed_forward_class, mixer_class,
                    norm_class, position_class, register_arrangement,
@@ -10,4 +10,5 @@ from .base import (Arrangement, FeedForward, Mixer, Norm, PagedNeed, PositionEnc
                    register_position)
 from .spec import (AttentionSpec, BlockSpec, FeedForwardSpec, LayerCall, MixerSpec,
                    ModelSpec, NormSpec, ParamDecl, PositionSpec, ShortConvSpec, SwiGLUSpec,
-                   DenseSpec, MinGRUSpec, MixedAttentionSpec, LatentAttentionSpec, MoESpec)
+                   DenseSpec, MinGRUSpec, MixedAttentionSpec, LatentAttentionSpec, MoESpec,
+                   GatedDeltaSpec, GluClampSpec)

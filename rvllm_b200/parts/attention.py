@@ -25,6 +25,15 @@ head, no weight).  A query temperature (`q_temp` = (coef, every)): the query at 
 multiplied by 1 + coef ln(floor((p + 1) / every) + 1), so scores grow slowly with the length
 of the context.  With the unit norm, the temperature or a value size of its own, norm,
 temperature and the cache write are `ops.qk_unit_write` after the one q|k|v product.
+
+A third form (`_prepared`), chosen by any of: biases on the q, k and v projections (`bias`); a
+norm over the whole query projection and one over the whole key projection, before the split
+into heads (`qk_norm` of kind "rms_full"); a rotation of neighbouring dimensions (position
+kind "rope_pairs"); value mixing (`value_mix`): the first such call of a step keeps its values
+("source"), every later one caches v <- (1 - l) v + l v_source with its learned scalar l.  The
+q|k|v product stays float32 and one kernel (`ops.qkv_full_norm_rope_write`) adds the biases,
+normalises, rotates, mixes and writes the cache.  A sink, a window and a value size of its own
+go with it.
 """
 from __future__ import annotations
 
@@ -41,7 +50,9 @@ class Attention(Mixer):
     def _names(spec):
         n = spec.names
         return {k: n.get(k, k + ".weight") for k in
-                ("q_proj", "k_proj", "v_proj", "out_proj", "q_norm", "k_norm", "sink")}
+                ("q_proj", "k_proj", "v_proj", "out_proj", "q_norm", "k_norm", "sink")} | \
+            {k: n.get(k, d) for k, d in (("q_bias", "q_proj.bias"), ("k_bias", "k_proj.bias"),
+                                         ("v_bias", "v_proj.bias"), ("vmix", "vmix"))}
 
     @staticmethod
     def params(spec: AttentionSpec, owns_cache: bool = True):
@@ -54,9 +65,20 @@ class Attention(Mixer):
             p[n["k_proj"]] = ParamDecl((kd, spec.hidden), "linear")
             p[n["v_proj"]] = ParamDecl((spec.num_kv_heads * dv, spec.hidden), "linear")
         if Attention._weighted_norm(spec):
-            p[n["q_norm"]] = ParamDecl((spec.head_dim,), "norm")
+            full = spec.qk_norm.kind == "rms_full"
+            p[n["q_norm"]] = ParamDecl((qd if full else spec.head_dim,), "norm")
             if owns_cache:
-                p[n["k_norm"]] = ParamDecl((spec.head_dim,), "norm")
+                p[n["k_norm"]] = ParamDecl((kd if full else spec.head_dim,), "norm")
+        if spec.bias:
+            p[n["q_bias"]] = ParamDecl((qd,), "bias")
+            if owns_cache:
+                p[n["k_bias"]] = ParamDecl((kd,), "bias")
+                p[n["v_bias"]] = ParamDecl((spec.num_kv_heads * dv,), "bias")
+        if spec.value_mix is not None:
+            if spec.value_mix not in ("source", "mix"):
+                raise ValueError(f"attention: value_mix is 'source' or 'mix', "
+                                 f"got {spec.value_mix!r}")
+            p[n["vmix"]] = ParamDecl((), "normal", mean=0.5, std=0.2)
         if spec.sinks:
             p[n["sink"]] = ParamDecl((spec.num_heads,), "normal", mean=0.0, std=1.0)
         return p
@@ -64,6 +86,12 @@ class Attention(Mixer):
     @staticmethod
     def _weighted_norm(spec) -> bool:
         return spec.qk_norm is not None and spec.qk_norm.kind != "rms_unit"
+
+    @staticmethod
+    def _prepared(spec) -> bool:
+        """Whether the layer takes the form served by `ops.qkv_full_norm_rope_write`."""
+        return spec.bias or spec.value_mix is not None or spec.position.kind == "rope_pairs" \
+            or (spec.qk_norm is not None and spec.qk_norm.kind == "rms_full")
 
     @staticmethod
     def _plain(spec) -> bool:
@@ -116,6 +144,14 @@ class Attention(Mixer):
             if self.has_kv:
                 self.k_norm = tensors[n["k_norm"]].to(torch.float32).contiguous()
         self.position = position_class(spec.position.kind)(spec.position, q.device)
+        self.bias = self.vmix = None
+        if self._prepared(spec):
+            self._check_prepared(spec)
+            if spec.bias:
+                self.bias = torch.cat([tensors[n[k]].to(torch.float32) for k in
+                                       ("q_bias", "k_bias", "v_bias")]).contiguous()
+            if spec.value_mix == "mix":
+                self.vmix = tensors[n["vmix"]].to(torch.float32).reshape(1).contiguous()
         self.scale = spec.scale if spec.scale is not None else 1.0 / math.sqrt(spec.head_dim)
 
     def forward(self, normed, ctx, cache):
@@ -125,6 +161,8 @@ class Attention(Mixer):
             raise ValueError("attention: this call owns a cache but the block has no "
                              "key and value projections")
         group = ctx.groups[cache.group]
+        if self._prepared(s):
+            return self._forward_prepared(normed, ctx, cache, group)
         if not self._plain(s):
             return self._forward_options(normed, ctx, cache, group)
         qkv = self.ops.linear_qk_norm_rope_write(
@@ -156,6 +194,47 @@ class Attention(Mixer):
         self.ops.paged_attention(rows, s.num_heads, s.num_kv_heads, s.head_dim,
                                  cache.k, cache.v, ctx, group, self.scale, s.window, out,
                                  sinks=self.sinks, v_head_dim=self.v_dim)
+        return self.ops.linear(out, self.w_out, out_dtype=self.dtype)
+
+
+    CARRY_VALUES = "attention.source_values"
+
+    def _check_prepared(self, spec):
+        if not self.has_kv:
+            raise ValueError("attention: this form makes its own keys and values")
+        if spec.q_temp is not None or (spec.qk_norm is not None and
+                                       spec.qk_norm.kind not in ("rms_full",)):
+            raise ValueError("attention: biases, a whole-projection norm, a pairwise rotation "
+                             "and value mixing go with no other q/k norm and no temperature")
+        if spec.position.kind not in ("rope_pairs", "none"):
+            raise ValueError("attention: this form turns neighbouring dimensions or none")
+
+    def _forward_prepared(self, normed, ctx, cache, group):
+        s = self.spec
+        if not cache.owns:
+            raise ValueError("attention: this form makes its own keys and values")
+        n = normed.shape[0]
+        rows = self.ops.linear(normed, self.w_qkv, out_dtype=torch.float32)
+        q = self.ops.new_rows(n, s.num_heads * s.head_dim, self.dtype, normed.device)
+        first_in = first_out = None
+        if s.value_mix == "source":
+            first_out = torch.empty((n, s.num_kv_heads * self.v_dim), dtype=torch.float32,
+                                    device=normed.device)
+            ctx.carry[self.CARRY_VALUES] = first_out
+        elif s.value_mix == "mix":
+            first_in = ctx.carry.get(self.CARRY_VALUES)
+            if first_in is None or first_in.shape != (n, s.num_kv_heads * self.v_dim):
+                raise ValueError("attention: values are mixed with those of an earlier call of "
+                                 "the step, and none of this shape ran")
+        freq, rot_dims = (None, 0) if s.position.kind == "none" else self.position.frequencies()
+        self.ops.qkv_full_norm_rope_write(
+            rows, self.bias, s.num_heads, s.num_kv_heads, s.head_dim, self.v_dim, self.q_norm,
+            self.k_norm, s.qk_norm.eps if s.qk_norm is not None else 0.0, freq, rot_dims,
+            ctx.positions, group.slot_mapping, q, cache.k, cache.v, first_in, first_out, self.vmix)
+        out = self.ops.new_rows(n, s.num_heads * self.v_dim, self.dtype, normed.device)
+        self.ops.paged_attention(q, s.num_heads, s.num_kv_heads, s.head_dim, cache.k, cache.v,
+                                 ctx, group, self.scale, s.window, out, sinks=self.sinks,
+                                 v_head_dim=self.v_dim)
         return self.ops.linear(out, self.w_out, out_dtype=self.dtype)
 
 

@@ -172,6 +172,8 @@ class Stream:
     resid: object                   # float32 [N, hidden]
     pending: Optional[object]       # [N, hidden], not yet added
     pending_norm: Optional[object] = None   # a Norm `pending` has to pass through first
+    pending_hyper: Optional[tuple] = None   # (mix [S, S], out [S]): how `pending` enters the
+                                            # streams of a block with hyper-connections
 
 
 _MIXERS: Dict[str, type] = {}

@@ -9,8 +9,8 @@ from __future__ import annotations
 
 import torch
 
-from .base import FeedForward, register_feed_forward
-from .spec import DenseSpec, MoESpec, ParamDecl, SwiGLUSpec
+from .base import FeedForward, feed_forward_class, register_feed_forward
+from .spec import DenseSpec, GluClampSpec, MoESpec, ParamDecl, SwiGLUSpec
 
 
 class SwiGLU(FeedForward):
@@ -85,6 +85,55 @@ class Dense(FeedForward):
 register_feed_forward("dense", Dense)
 
 
+class GluClamp(FeedForward):
+    """down(g * sigmoid(alpha g) * (u + 1)) with g = min(gate(x), limit) and
+    u = clamp(up(x), -limit, limit); with `bias` the three products have biases (the tensor's
+    name plus ".b").  gate and up are one [2F, hidden] product; their biases, the clamps and
+    the activation are one kernel."""
+
+    @staticmethod
+    def _names(spec):
+        n = spec.names
+        return {k: n.get(k, k) for k in ("gate", "up", "down")}
+
+    @staticmethod
+    def params(spec: GluClampSpec):
+        if not spec.limit > 0:
+            raise ValueError(f"glu_clamp: the limit must be positive, got {spec.limit}")
+        n = GluClamp._names(spec)
+        p = {n["gate"]: ParamDecl((spec.ffn_dim, spec.hidden), "linear"),
+             n["up"]: ParamDecl((spec.ffn_dim, spec.hidden), "linear"),
+             n["down"]: ParamDecl((spec.hidden, spec.ffn_dim), "linear")}
+        if spec.bias:
+            p[n["gate"] + ".b"] = ParamDecl((spec.ffn_dim,), "bias")
+            p[n["up"] + ".b"] = ParamDecl((spec.ffn_dim,), "bias")
+            p[n["down"] + ".b"] = ParamDecl((spec.hidden,), "bias")
+        return p
+
+    def __init__(self, spec: GluClampSpec, tensors, ops, dtype):
+        self.spec = spec
+        self.ops = ops
+        self.dtype = dtype
+        n = self._names(spec)
+        gate = tensors[n["gate"]]
+        self.gate_up = torch.cat([gate, tensors[n["up"]].to(gate.dtype)], dim=0).contiguous()
+        self.down = tensors[n["down"]].contiguous()
+        self.bias_in = self.bias_out = None
+        if spec.bias:
+            self.bias_in = torch.cat([tensors[n["gate"] + ".b"].to(torch.float32),
+                                      tensors[n["up"] + ".b"].to(torch.float32)]).contiguous()
+            self.bias_out = tensors[n["down"] + ".b"].to(torch.float32).contiguous()
+
+    def forward(self, normed, ctx):
+        gate_up = self.ops.linear(normed, self.gate_up, out_dtype=self.dtype)
+        act = self.ops.new_rows(normed.shape[0], self.spec.ffn_dim, self.dtype, normed.device)
+        self.ops.glu_clamp(gate_up, self.bias_in, act, self.spec.limit, self.spec.alpha)
+        return self.ops.linear(act, self.down, bias=self.bias_out, out_dtype=self.dtype)
+
+
+register_feed_forward("glu_clamp", GluClamp)
+
+
 class MoE(FeedForward):
     """A mixture of SwiGLU experts (`MoESpec`).  For a token x:
 
@@ -100,8 +149,14 @@ class MoE(FeedForward):
     experts (few tokens) and grouped matrix products over the tokens sorted by expert.  A
     token's result is a sum over its own experts in the order they were chosen, so it does not
     depend on what else is in the batch.
+
+    Options of the spec: scores that are the softmax of the router logits over all experts;
+    chosen scores that are not divided by their sum; a factor on every weight; experts of the
+    clamped form (`GluClamp`); a shared feed-forward that every token passes, whose output is
+    where the experts' weighted sum starts.
     """
-    SCORES = ("sigmoid",)
+    SCORES = ("sigmoid", "softmax")
+    ACTIVATIONS = ("swiglu", "glu_clamp")
 
     @staticmethod
     def _names(spec):
@@ -116,6 +171,9 @@ class MoE(FeedForward):
     def _check(spec: MoESpec):
         if spec.score not in MoE.SCORES:
             raise ValueError(f"unknown router score {spec.score!r} (known: {MoE.SCORES})")
+        if spec.activation not in MoE.ACTIVATIONS:
+            raise ValueError(f"unknown expert activation {spec.activation!r} "
+                             f"(known: {MoE.ACTIVATIONS})")
         if spec.experts < 1 or not 1 <= spec.top <= spec.experts:
             raise ValueError(f"a mixture of {spec.experts} experts cannot use {spec.top} a token")
         if spec.groups < 1 or spec.experts % spec.groups or not 1 <= spec.keep <= spec.groups:
@@ -135,7 +193,12 @@ class MoE(FeedForward):
             p[n[(e, "gate")]] = ParamDecl((spec.ffn_dim, spec.hidden), "linear")
             p[n[(e, "up")]] = ParamDecl((spec.ffn_dim, spec.hidden), "linear")
             p[n[(e, "down")]] = ParamDecl((spec.hidden, spec.ffn_dim), "linear")
+        if spec.shared is not None:
+            for k, d in feed_forward_class(spec.shared.kind).params(spec.shared).items():
+                p[MoE.SHARED_PREFIX + k] = d
         return p
+
+    SHARED_PREFIX = "shared."
 
     def __init__(self, spec: MoESpec, tensors, ops, dtype):
         self._check(spec)
@@ -152,6 +215,11 @@ class MoE(FeedForward):
             for e in range(spec.experts)]).contiguous()          # [E, 2F, W]: gate f, up f, ...
         self.down = torch.stack([tensors[n[(e, "down")]].to(first.dtype)
                                  for e in range(spec.experts)]).contiguous()   # [E, W, F]
+        self.shared = None
+        if spec.shared is not None:
+            sub = {k[len(self.SHARED_PREFIX):]: v for k, v in tensors.items()
+                   if k.startswith(self.SHARED_PREFIX)}
+            self.shared = feed_forward_class(spec.shared.kind)(spec.shared, sub, ops, dtype)
 
     def forward(self, normed, ctx):
         s = self.spec
@@ -159,10 +227,18 @@ class MoE(FeedForward):
         ids = torch.empty((n, s.top), dtype=torch.int32, device=normed.device)
         weights = torch.empty((n, s.top), dtype=torch.float32, device=normed.device)
         # the router's product and the choice: one kernel
+        extra = {}
+        if s.score != "sigmoid" or not s.renormalize or s.route_scale != 1.0:
+            extra = dict(score=s.score, renormalize=s.renormalize, route_scale=s.route_scale)
         self.ops.moe_route(normed, self.router, s.groups, s.keep, s.group_top, s.weight_eps,
-                           ids, weights)
+                           ids, weights, **extra)
         out = self.ops.new_rows(n, s.hidden, self.dtype, normed.device)
-        self.ops.moe_experts(normed, ids, weights, self.gate_up, self.down, out)
+        extra = {}
+        if s.activation != "swiglu":
+            extra = dict(activation=s.activation, limit=s.limit, alpha=s.alpha)
+        if self.shared is not None:
+            extra["addend"] = self.shared.forward(normed, ctx).contiguous()
+        self.ops.moe_experts(normed, ids, weights, self.gate_up, self.down, out, **extra)
         return out
 
 

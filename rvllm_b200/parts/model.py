@@ -43,6 +43,13 @@ def param_decls(spec: ModelSpec) -> Dict[str, ParamDecl]:
 
 
 def validate_order(spec: ModelSpec) -> None:
+    for b in spec.layers:
+        if b.streams != spec.streams:
+            raise ValueError(f"a block keeps {b.streams} residual streams, "
+                             f"the model {spec.streams}")
+        if (b.arrangement == "hyper_pre_norm") != (spec.streams >= 1):
+            raise ValueError("blocks with several residual streams are 'hyper_pre_norm' "
+                             "blocks, and only they")
     for pos, call in enumerate(spec.order):
         if not 0 <= call.layer < len(spec.layers):
             raise ValueError(f"run order entry {pos} names layer {call.layer}, "
@@ -111,8 +118,14 @@ class Model:
         if ctx.logit_rows.shape[0] == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32,
                                device=self.device)
-        normed = self.final_norm.add_norm(stream.resid, stream.pending, ctx,
-                                          rows=ctx.logit_rows, delta_norm=stream.pending_norm)
+        if self.spec.streams >= 1:
+            from .hyper import hyper_between
+            _, normed = hyper_between(self.ops, stream, None, self.final_norm, self.dtype,
+                                      self.spec.streams, rows=ctx.logit_rows)
+        else:
+            normed = self.final_norm.add_norm(stream.resid, stream.pending, ctx,
+                                              rows=ctx.logit_rows,
+                                              delta_norm=stream.pending_norm)
         logits = self.ops.linear(normed, self.head, out_dtype=torch.float32)
         if self.spec.logit_softcap:
             self.ops.softcap(logits, self.spec.logit_softcap)

@@ -63,6 +63,42 @@ class PartialRope(PositionEncoding):
         return self.inv_freq, self.rot_dims
 
 
+class PairRope(PositionEncoding):
+    """A rotation of neighbouring dimensions: in each head the pair (2i, 2i + 1), i < rot_dims/2,
+    at position p turns by p * f_i with f_i = theta^(-2i/rot_dims); the dimensions from rot_dims
+    on pass.  With `scaling` = (factor, low, high, original) long wavelengths are stretched
+    (see `PositionSpec`).  As with `PartialRope` the kernels form the angle in float32 from
+    the position and `frequencies()`, so no longest context has to be known."""
+
+    def __init__(self, spec: PositionSpec, device):
+        dims = spec.rot_dims or spec.head_dim
+        if dims % 2 or dims > spec.head_dim or dims < 0 or spec.head_dim % 2:
+            raise ValueError(f"rope_pairs needs an even number of turning dimensions within an "
+                             f"even head size, got {dims} of {spec.head_dim}")
+        self.spec = spec
+        self.rot_dims = dims
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(spec.theta, dtype=torch.float64), -2.0 * i / max(dims, 1))
+        if spec.scaling is not None:
+            factor, low, high, original = spec.scaling
+            if not (factor > 0 and high > low and original > 0):
+                raise ValueError("rope_pairs: the scaling needs factor > 0, high > low and a "
+                                 "positive original length")
+            wavelength = 2.0 * torch.pi / f
+            s = (original / wavelength - low) / (high - low)
+            between = (1.0 - s) * f / factor + s * f
+            f = torch.where(wavelength < original / high, f,
+                            torch.where(wavelength > original / low, f / factor, between))
+        self.inv_freq = f.to(torch.float32).to(device).contiguous()
+
+    def rotation_table(self):
+        return None
+
+    def frequencies(self):
+        """(float32 [rot_dims/2] angle per position of each pair, rot_dims)"""
+        return self.inv_freq, self.rot_dims
+
+
 class NoPosition(PositionEncoding):
     def __init__(self, spec: PositionSpec, device):
         self.spec = spec
@@ -73,4 +109,5 @@ class NoPosition(PositionEncoding):
 
 register_position("rope", Rope)
 register_position("rope_partial", PartialRope)
+register_position("rope_pairs", PairRope)
 register_position("none", NoPosition)

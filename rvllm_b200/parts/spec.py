@@ -48,12 +48,18 @@ class NormSpec:
 @dataclass(frozen=True)
 class PositionSpec:
     """How positions enter the attention mixer. kind "none" applies nothing.
-    `rot_dims` (kind "rope_partial"): only the first rot_dims dimensions of a head turn."""
+    `rot_dims` (kinds "rope_partial", "rope_pairs"): only the first rot_dims dimensions of a
+    head turn.  Kind "rope_pairs" turns neighbouring dimensions (2i, 2i + 1) together, and
+    `scaling` = (factor, low, high, original) stretches its long wavelengths: with wavelength
+    l = 2 pi / f a frequency stays when l < original / high, becomes f / factor when
+    l > original / low, and in between is (1 - s) f / factor + s f with
+    s = (original / l - low) / (high - low)."""
     kind: str
     head_dim: int = 0
     theta: float = 0.0
     max_position: int = 0
     rot_dims: int = 0
+    scaling: Optional[Tuple[float, float, float, int]] = None
 
 
 @dataclass(frozen=True)
@@ -82,6 +88,12 @@ class AttentionSpec(MixerSpec):
                                                 # (tensor "sink" [heads])
     q_temp: Optional[Tuple[float, int]] = None  # (coef, every): the query at position p is
                                                 # multiplied by 1 + coef ln(floor((p+1)/every) + 1)
+    # `qk_norm` of kind "rms_full" is one RMSNorm over the whole query projection (and one over
+    # the whole key projection) before the split into heads, with weights of those sizes.
+    bias: bool = False                          # q, k and v projections have biases
+    value_mix: Optional[str] = None             # "source": this call's values are kept for the
+                                                # step; "mix": v <- (1 - l) v + l v_source with
+                                                # the learned scalar "vmix", before the cache
 
 
 @dataclass(frozen=True)
@@ -137,6 +149,25 @@ class MinGRUSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class GatedDeltaSpec(MixerSpec):
+    """The gated delta rule with one decay per key channel.  `num_kv_heads` query/key heads of
+    size `head_dim`, `num_heads` value heads of size `v_head_dim`; q, k and v pass a causal
+    convolution of `taps` taps and silu; the decay and the output gate are products of rank
+    `decay_rank` and `gate_rank`; `unit_eps` sits under the root of the unit norms of q and
+    k, `norm_eps` under that of the output norm."""
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    taps: int = 0
+    decay_rank: int = 0
+    gate_rank: int = 0
+    norm_eps: float = 1e-6
+    unit_eps: float = 1e-6
+    names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+
+
+@dataclass(frozen=True)
 class ShortConvSpec(MixerSpec):
     taps: int = 0                               # filter length; the state holds taps-1 rows
     bias: bool = False
@@ -164,6 +195,17 @@ class DenseSpec(FeedForwardSpec):
 
 
 @dataclass(frozen=True)
+class GluClampSpec(FeedForwardSpec):
+    """down(g * sigmoid(alpha g) * (u + 1)) with g = min(gate(x), limit) and
+    u = clamp(up(x), -limit, limit); `bias`: the three products have biases."""
+    ffn_dim: int = 0
+    limit: float = 0.0
+    alpha: float = 1.702
+    bias: bool = False
+    names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+
+
+@dataclass(frozen=True)
 class MoESpec(FeedForwardSpec):
     """A mixture of `experts` SwiGLU feed-forwards of size `ffn_dim`, of which a token uses
     `top`.  score: how router logits become scores ("sigmoid").  `groups` > 1: the experts
@@ -171,7 +213,11 @@ class MoESpec(FeedForwardSpec):
     `group_top` largest scores, and only experts of the `keep` best groups can be chosen.
     The chosen experts' scores, divided by their sum + `weight_eps`, weigh their outputs.
     Tensors: "router" [experts, hidden]; per expert e "e<e>.gate", "e<e>.up" [ffn_dim, hidden],
-    "e<e>.down" [hidden, ffn_dim]."""
+    "e<e>.down" [hidden, ffn_dim].
+    Options: score "softmax" (over all experts); `renormalize` false leaves the chosen scores
+    undivided; `route_scale` multiplies every weight; `activation` "glu_clamp" gives the experts
+    the clamped form of `GluClampSpec` with `limit` and `alpha`; `shared` is a feed-forward
+    that every token passes as well and whose output is added (tensors under "shared.")."""
     ffn_dim: int = 0
     experts: int = 0
     top: int = 0
@@ -180,6 +226,12 @@ class MoESpec(FeedForwardSpec):
     group_top: int = 2
     score: str = "sigmoid"
     weight_eps: float = 1e-20
+    renormalize: bool = True
+    route_scale: float = 1.0
+    activation: str = "swiglu"
+    limit: float = 0.0
+    alpha: float = 1.702
+    shared: Optional[FeedForwardSpec] = None
     names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
 
 
@@ -196,6 +248,10 @@ class BlockSpec:
     reference's `post_attn_norm` and `post_ffn_norm`, src/model.rs:571, 581; LFM2 has
     neither).  The *_prefix fields say where the mixer's and the feed-forward's tensors
     are found in the file.
+
+    "hyper_pre_norm" keeps `streams` >= 1 copies of the residual (hyper-connections); `hyper` maps
+    the places "mixer" and "ffn" to the prefix of that sub-layer's three tensors (".in" [S],
+    ".out" [S], ".mix" [S, S]).
     """
     arrangement: str
     mixer: MixerSpec
@@ -203,6 +259,8 @@ class BlockSpec:
     norms: Mapping[str, Tuple[NormSpec, object]] = field(hash=False)
     mixer_prefix: str = ""
     ffn_prefix: str = ""
+    streams: int = 0
+    hyper: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
 
 
 @dataclass(frozen=True)
@@ -228,5 +286,8 @@ class ModelSpec:
     head_name: Optional[str]                    # None: the head is the embedding table
     embedding_scale: Optional[float] = None
     logit_softcap: Optional[float] = None       # c: logits <- c tanh(logits / c)
+    streams: int = 0                            # copies of the residual (hyper-connections; 0:
+                                                # the one plain residual); the final norm
+                                                # reads their sum
     bos_token_id: Optional[int] = None
     eos_token_id: Optional[int] = None

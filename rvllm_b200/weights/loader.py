@@ -40,6 +40,11 @@ def open_folder(folder: str) -> List[SafetensorsFile]:
     raise WeightsError(f"{folder}: no {SINGLE} (nor {INDEX}) in this model folder")
 
 
+def tensor_shapes(folder: str) -> Dict[str, tuple]:
+    """name -> shape of every tensor in the folder's files (their headers only)."""
+    return {name: tuple(f.shape(name)) for f in open_folder(folder) for name in f.names()}
+
+
 def device_dtype(stored: torch.dtype, compute: torch.dtype, integer: bool) -> torch.dtype:
     if integer:
         return torch.int32

@@ -324,12 +324,14 @@ class PlainOps:
         x.copy_((_f(x) * g).to(x.dtype))
 
     # ---- mixture of experts ---------------------------------------------------------------
-    def moe_select(self, logits, groups, keep, group_top, weight_eps, ids, weights):
+    def moe_select(self, logits, groups, keep, group_top, weight_eps, ids, weights,
+                   score="sigmoid", renormalize=True, route_scale=1.0):
         n, E = logits.shape
         top = ids.shape[1]
         size = E // groups
         for t in range(n):
-            s = torch.sigmoid(_f(logits[t]))
+            s = torch.sigmoid(_f(logits[t])) if score == "sigmoid" else \
+                torch.softmax(_f(logits[t]), dim=0)
             allowed = s.clone()
             if groups > 1:
                 gs = s.reshape(groups, size).sort(dim=1, descending=True).values[:, :group_top].sum(1)
@@ -339,25 +341,144 @@ class PlainOps:
                         allowed[g * size:(g + 1) * size] = -1.0
             chosen = torch.sort(allowed, descending=True, stable=True).indices[:top]
             ids[t] = chosen.to(torch.int32)
-            weights[t] = s[chosen] / (s[chosen].sum() + weight_eps)
+            w = s[chosen] / (s[chosen].sum() + weight_eps) if renormalize else s[chosen]
+            weights[t] = w * route_scale
 
-    def moe_route(self, x, router, groups, keep, group_top, weight_eps, ids, weights):
-        self.moe_select(_f(x) @ _f(router).t(), groups, keep, group_top, weight_eps, ids, weights)
+    def moe_route(self, x, router, groups, keep, group_top, weight_eps, ids, weights, **options):
+        self.moe_select(_f(x) @ _f(router).t(), groups, keep, group_top, weight_eps, ids, weights,
+                        **options)
 
-    def moe_experts(self, x, ids, weights, gate_up, down, out):
+    def moe_experts(self, x, ids, weights, gate_up, down, out, activation="swiglu", limit=0.0,
+                    alpha=1.0, addend=None):
         n, top = ids.shape
         F = down.shape[2]
         y = torch.zeros((n, out.shape[1]), dtype=torch.float32)
+        if addend is not None:
+            y += _f(addend)
         for t in range(n):
             for k in range(top):
                 e = int(ids[t, k])
                 gu = _f(gate_up[e]) @ _f(x[t])               # gate and up rows alternate
-                act = (torch.nn.functional.silu(gu[0::2]) * gu[1::2]).to(x.dtype)
+                if activation == "glu_clamp":
+                    g, u = gu[0::2].clamp(max=limit), gu[1::2].clamp(-limit, limit)
+                    act = (g * torch.sigmoid(alpha * g) * (u + 1)).to(x.dtype)
+                else:
+                    act = (torch.nn.functional.silu(gu[0::2]) * gu[1::2]).to(x.dtype)
                 y[t] += float(weights[t, k]) * (_f(down[e]) @ _f(act))
         out.copy_(y.to(out.dtype))
 
     def softcap(self, logits, cap):
         logits.copy_(cap * torch.tanh(logits / cap))
+
+    # ---- hyper-connections -----------------------------------------------------------
+    def hyper_norm(self, src, dst, delta, mix, out_w, in_w, weight, eps, out, rows=None):
+        x = src if src.dim() == 3 else None
+        if x is None:
+            S = dst.shape[1] if dst is not None else (in_w.shape[0] if in_w is not None else 1)
+            x = src.unsqueeze(1).expand(-1, S, -1)
+        x = x.clone()
+        if delta is not None:
+            x = torch.einsum("st,nsw->ntw", _f(mix), x) + _f(out_w)[None, :, None] * _f(delta)[:, None, :]
+        if dst is not None:
+            dst.copy_(x)
+        if rows is not None:
+            x = x[rows.long()]
+        u = x.sum(1) if in_w is None else torch.einsum("t,ntw->nw", _f(in_w), x)
+        rms = (u.pow(2).mean(dim=-1, keepdim=True) + eps).sqrt()
+        out.copy_((u / rms * _f(weight)).to(out.dtype))
+
+    # ---- whole-projection q/k norm, pairwise rotation, value mixing, cache write -----
+    def qkv_full_norm_rope_write(self, rows, bias, num_heads, num_kv_heads, head_dim, v_head_dim,
+                                 q_weight, k_weight, eps, freq, rot_dims, positions, slot_mapping,
+                                 q_out, k_cache, v_cache, v_first_in=None, v_first_out=None,
+                                 lam=None):
+        n = rows.shape[0]
+        Q, K = num_heads * head_dim, num_kv_heads * head_dim
+        x = _f(rows) if bias is None else _f(rows) + _f(bias)
+        q, k, v = x[:, :Q], x[:, Q:Q + K], x[:, Q + K:]
+
+        def norm(t, w):
+            if w is None:
+                return t
+            return t / (t.pow(2).mean(dim=-1, keepdim=True) + eps).sqrt() * _f(w)
+
+        def turn(t, heads):
+            t = t.reshape(n, heads, head_dim).clone()
+            if rot_dims:
+                ang = positions.to(torch.float32)[:, None] * _f(freq)[None, :]
+                c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+                a, b = t[..., 0:rot_dims:2].clone(), t[..., 1:rot_dims:2].clone()
+                t[..., 0:rot_dims:2] = a * c - b * s
+                t[..., 1:rot_dims:2] = b * c + a * s
+            return t.reshape(n, heads * head_dim)
+
+        q = turn(norm(q, q_weight), num_heads)
+        k = turn(norm(k, k_weight), num_kv_heads)
+        if v_first_out is not None:
+            v_first_out.copy_(v)
+        if v_first_in is not None:
+            v = (1 - _f(lam)) * v + _f(lam) * _f(v_first_in)
+        q_out.copy_(q.to(q_out.dtype))
+        kc = k_cache.view(-1, K)
+        vc = v_cache.view(-1, v.shape[1])
+        for t in range(n):
+            slot = int(slot_mapping[t])
+            if slot >= 0:
+                kc[slot] = k[t].to(kc.dtype)
+                vc[slot] = v[t].to(vc.dtype)
+
+    # ---- gated delta rule ------------------------------------------------------------
+    def gated_delta_record(self, heads, kv_heads, dim, vdim, taps):
+        return (taps - 1) * (2 * kv_heads * dim + heads * vdim) + heads * dim * vdim
+
+    def gated_delta(self, proj, lowrank, filt, a_log, dt_bias, norm_w, state, ctx, out, heads,
+                    kv_heads, dim, vdim, taps, unit_eps, eps):
+        H, G, d, dv = heads, kv_heads, dim, vdim
+        C = 2 * G * d + H * dv
+        q_start = ctx.q_start.tolist()
+        slots = ctx.state_slot.tolist()
+        p, low = _f(proj), _f(lowrank)
+        for r in range(ctx.n_reqs):
+            a, b = q_start[r], q_start[r + 1]
+            if slots[r] < 0 or a == b:
+                continue
+            rec = state[slots[r]]
+            old = rec[:(taps - 1) * C].reshape(taps - 1, C).clone()
+            S = rec[(taps - 1) * C:].reshape(H, d, dv).clone()
+            rows = torch.cat([old, p[a:b, :C]], dim=0)
+            n = b - a
+            conv = torch.zeros(n, C)
+            for j in range(taps):
+                conv = conv + rows[j:j + n] * _f(filt)[:, j]
+            act = conv * torch.sigmoid(conv)
+            for i in range(n):
+                t = a + i
+                q = act[i, :G * d].reshape(G, d)
+                k = act[i, G * d:2 * G * d].reshape(G, d)
+                v = act[i, 2 * G * d:].reshape(H, dv)
+                q = q / (q.pow(2).sum(-1, keepdim=True) + unit_eps).sqrt() / math.sqrt(d)
+                k = k / (k.pow(2).sum(-1, keepdim=True) + unit_eps).sqrt()
+                beta = torch.sigmoid(p[t, C:C + H])
+                decay = torch.exp(-torch.exp(_f(a_log))[:, None] * torch.nn.functional.softplus(
+                    low[t, :H * d] + _f(dt_bias)).reshape(H, d))
+                gate = torch.sigmoid(low[t, H * d:H * d + H * dv]).reshape(H, dv)
+                for h in range(H):
+                    kh, qh = k[h // (H // G)], q[h // (H // G)]
+                    S[h] = decay[h][:, None] * S[h]
+                    u = beta[h] * (v[h] - S[h].t() @ kh)
+                    S[h] = S[h] + torch.outer(kh, u)
+                    o = S[h].t() @ qh
+                    o = o / (o.pow(2).mean() + eps).sqrt() * _f(norm_w) * gate[h]
+                    out[t, h * dv:(h + 1) * dv] = o.to(out.dtype)
+            rec[:(taps - 1) * C] = rows[n:].reshape(-1)
+            rec[(taps - 1) * C:] = S.reshape(-1)
+
+    # ---- clamped gated activation ----------------------------------------------------
+    def glu_clamp(self, gate_up, bias, out, limit, alpha):
+        f = out.shape[1]
+        x = _f(gate_up) if bias is None else _f(gate_up) + _f(bias)
+        g, u = x[:, :f].clamp(max=limit), x[:, f:].clamp(-limit, limit)
+        out.copy_((g * torch.sigmoid(alpha * g) * (u + 1)).to(out.dtype))
 
     # ---- sampling --------------------------------------------------------------------
     def argmax(self, logits):
