@@ -103,7 +103,7 @@ def write_streamed(path: str, layout: List[Tuple[str, Tuple[int, ...], torch.dty
                 raise ValueError(f"tensor {name!r}: produced {tuple(t.shape)} {t.dtype}, "
                                  f"layout says {tuple(shape)} {dtype}")
             if t.numel():
-                f.write(t.contiguous().view(torch.uint8).numpy().tobytes())
+                f.write(t.contiguous().reshape(-1).view(torch.uint8).numpy().tobytes())
     os.replace(tmp, path)
 
 
