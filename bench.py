@@ -35,6 +35,9 @@ steps it holds 4096 - K tokens, then K steps are timed with CUDA events and end 
 
 `--only bizenex` (not part of the default run) measures Bizenex (latent and grouped-query
 attention with sinks, a mixture of experts) beside an all-attention LFM2 of equal sizes.
+`--only vifanex` (not part of the default run) measures Vifanex (gated delta rule and windowed
+attention in turn on several residual streams, a softmax-routed mixture with a shared expert)
+beside Bizenex at equal sizes.
 `--only retorax` (not part of the default run) measures another design, Retorax, beside LFM2
 at equal sizes (width 1024 and 2048, eight layers): a 2,048-token prompt, single tokens at
 batch 8 and 64, and the device time of every kernel of a step against its roofline.
@@ -881,6 +884,44 @@ def bizenex_config(sz):
             "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": layers}
 
 
+VIFANEX_SIZES = {
+    # gated delta rule and windowed grouped-query attention in turn on `streams` residual
+    # streams; the first layer's feed-forward is dense (as wide as the experts a token uses),
+    # the others are mixtures with a shared expert.  The fields Bizenex reads are here too, so
+    # that it runs beside at equal sizes.
+    "w1024": {"width": 1024, "layers": 8, "heads": 16, "kv": 4, "dim": 64, "rank": 128, "window": 1024,
+              "delta_heads": 8, "delta_kv": 4, "delta_dim": 128, "low_rank": 64, "taps": 4, "streams": 4,
+              "experts": 16, "top": 4, "groups": (4, 2), "ff": 1024, "vocab": 32768},
+    "w2048": {"width": 2048, "layers": 8, "heads": 32, "kv": 8, "dim": 64, "rank": 128, "window": 1024,
+              "delta_heads": 16, "delta_kv": 8, "delta_dim": 128, "low_rank": 64, "taps": 4, "streams": 4,
+              "experts": 16, "top": 4, "groups": (4, 2), "ff": 2048, "vocab": 32768},
+}
+
+
+def vifanex_config(sz):
+    layers = []
+    moe = {"kind": "moe", "expert": {"ff": sz["ff"], "limit": 7.0},
+           "router": {"experts": sz["experts"], "top": sz["top"], "scale": 1.5,
+                      "groups": {"count": sz["groups"][0], "keep": sz["groups"][1]}},
+           "shared": {"ff": sz["ff"], "limit": 7.0}}
+    for i in range(sz["layers"]):
+        mlp = {"kind": "dense", "ff": sz["top"] * sz["ff"], "limit": 7.0} if i == 0 else moe
+        if i % 2 == 0:
+            mixer = {"heads": sz["delta_heads"], "kv_heads": sz["delta_kv"], "dim": sz["delta_dim"],
+                     "vdim": sz["delta_dim"], "conv": sz["taps"], "decay_rank": sz["low_rank"],
+                     "gate_rank": sz["low_rank"]}
+            layers.append({"type": "channel_delta", "mixer": mixer, "mlp": mlp})
+        else:
+            mixer = {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"],
+                     "scale": sz["dim"] ** -0.5, "mask": {"size": sz["window"]}, "v_mix": True,
+                     "rot": {"dims": sz["dim"], "base": 10000.0,
+                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+            layers.append({"type": "attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Vifanex", "vocab": sz["vocab"], "width": sz["width"], "streams": sz["streams"],
+            "norm": {"eps": 1e-6}, "embedding": {"scale": sz["width"] ** 0.5}, "logit_softcap": 30.0,
+            "layers": layers}
+
+
 def lfm2_all_attention(sz):
     """LFM2 with the same width and layer count, attention in every layer with the same head
     counts and sizes, and a SwiGLU as wide as the experts a token uses together."""
@@ -909,7 +950,8 @@ class OpTimer:
     NAMES = ("embed", "add_rmsnorm", "add_layernorm", "linear", "linear_qk_norm_rope_write",
              "qk_norm_rope_write", "rope_partial_write", "paged_attention", "paged_attention_mixed",
              "short_conv", "mingru_scan", "swiglu", "xielu", "qk_unit_write", "latent_norm_write",
-             "heads_product", "sigmoid_gate", "moe_select", "moe_route", "moe_experts", "softcap")
+             "heads_product", "sigmoid_gate", "moe_select", "moe_route", "moe_experts", "softcap",
+             "hyper_norm", "qkv_full_norm_rope_write", "gated_delta", "glu_clamp")
 
     def __init__(self, torch, ops):
         self.torch, self.ops, self.events, self.saved = torch, ops, [], {}
@@ -946,7 +988,8 @@ class OpTimer:
 
 
 def run_designs(args, which="retorax"):
-    """Retorax (`--only retorax`) or Bizenex (`--only bizenex`) beside LFM2 at equal sizes:
+    """Retorax (`--only retorax`) or Bizenex (`--only bizenex`) beside LFM2, or Vifanex
+    (`--only vifanex`) beside Bizenex, at equal sizes:
     prompt and single-token throughput, and the device time of every kernel of one prompt step
     and one single-token step with its share of the roofline.  One JSON line."""
     import torch
@@ -959,13 +1002,17 @@ def run_designs(args, which="retorax"):
     out = {"only": which, "peaks": pk["source"], "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1)}
     gen = torch.Generator().manual_seed(0)
     T, CTX = 2048, 1024
-    sizes = RETORAX_SIZES if which == "retorax" else BIZENEX_SIZES
+    sizes = {"retorax": RETORAX_SIZES, "bizenex": BIZENEX_SIZES, "vifanex": VIFANEX_SIZES}[which]
     for size_name, sz in sizes.items():
         if args.design_size not in ("all", size_name):
             continue
         entry = {}
-        pair = (("retorax", retorax_config(sz)), ("lfm2", lfm2_like(sz))) if which == "retorax" \
-            else (("bizenex", bizenex_config(sz)), ("lfm2", lfm2_all_attention(sz)))
+        if which == "retorax":
+            pair = (("retorax", retorax_config(sz)), ("lfm2", lfm2_like(sz)))
+        elif which == "bizenex":
+            pair = (("bizenex", bizenex_config(sz)), ("lfm2", lfm2_all_attention(sz)))
+        else:
+            pair = (("vifanex", vifanex_config(sz)), ("bizenex", bizenex_config(sz)))
         for design, data in pair:
             cfg = config_from_dict(data)
             tmp = tempfile.mkdtemp(prefix="rvllm_bench_")
@@ -1035,8 +1082,8 @@ def run_designs(args, which="retorax"):
             entry[design] = res
             del model
             torch.cuda.empty_cache()
-        entry["rooflines"] = design_rooflines(sz, entry, pk, T, CTX) if which == "retorax" \
-            else bizenex_rooflines(sz, entry, pk, T, CTX)
+        entry["rooflines"] = {"retorax": design_rooflines, "bizenex": bizenex_rooflines,
+                              "vifanex": vifanex_rooflines}[which](sz, entry, pk, T, CTX)
         out[size_name] = entry
     print(json.dumps(out))
     return 0
@@ -1139,6 +1186,72 @@ def bizenex_rooflines(sz, entry, pk, T, CTX):
     return rows
 
 
+def vifanex_rooflines(sz, entry, pk, T, CTX):
+    """Per kernel pair (Vifanex's kernel, Bizenex's like kernel): device time of all calls in the
+    prompt step, and the time the roofline allows: bytes / measured copy rate for the elementwise
+    kernels, tensor FLOPs / measured GEMM rate for attention and the experts' products, and for
+    the delta rule's recurrence its float32 FLOPs (7 a state element a token) on the CUDA cores at
+    their nominal rate.  The recurrence has no like kernel in Bizenex; it stands alone."""
+    W, F, H, G, D, R = sz["width"], sz["ff"], sz["heads"], sz["kv"], sz["dim"], sz["rank"]
+    L, E, top, S = sz["layers"], sz["experts"], sz["top"], sz["streams"]
+    Hd, Gd, Dd, ranks, taps = sz["delta_heads"], sz["delta_kv"], sz["delta_dim"], sz["low_rank"], sz["taps"]
+    hbm = pk["hbm_gbs"] * 1e3                       # bytes per microsecond
+    tens = pk["bf16_tflops"] * 1e6                  # FLOPs per microsecond
+    fp32 = FP32_TFLOPS_NOMINAL * 1e6
+    n_delta, n_att = (L + 1) // 2, L // 2
+    n_lat = (L + 1) // 2                            # Bizenex: latent layers, grouped ones n_att
+    window = sz["window"]
+    pairs_w = sum(min(p + 1, window) for p in range(T))
+    pairs = T * (T + 1) // 2
+    C = 2 * Gd * Dd + Hd * Dd
+    ideal = {
+        # per call: S streams read and written, the pending rows read, the normalised rows written
+        "hyper_norm": 2 * L * T * W * (8 * S + 2 + 2) / hbm,
+        "add_layernorm": (2 * L + 1) * T * W * (4 + 4 + 2 + 2) / hbm,
+        # the float32 q|k|v rows read, q written, k and v written to the pages, the first values
+        "qkv_full_norm_rope_write": n_att * T * ((H + 2 * G) * D * 4 + (H + 2 * G) * D * 2 + G * D * 4) / hbm,
+        "qk_unit_write": n_att * T * ((H + G) * D * 4 + 2 * G * D * 2) / hbm,
+        "paged_attention": n_att * pairs_w * 4.0 * H * D / tens,
+        "paged_attention_bizenex": (n_lat * pairs * 4.0 * H * R + n_att * pairs * 4.0 * H * D) / tens,
+        # gate|up rows read, the activation written: the dense layer and the shared experts
+        "glu_clamp": (T * top * F * 6 + (L - 1) * T * F * 6) / hbm,
+        "sigmoid_gate": n_lat * T * H * D * 6 / hbm,
+        "moe_route": (L - 1) * T * (W * 2 + top * 8) / hbm,
+        "moe_route_bizenex": L * T * (W * 2 + top * 8) / hbm,
+        "moe_experts": (L - 1) * T * top * 6.0 * F * W / tens,
+        "moe_experts_bizenex": L * T * top * 6.0 * F * W / tens,
+        # the recurrence: decay, correction and read-out touch every state element of every token
+        "gated_delta": n_delta * max(T * Hd * 7.0 * Dd * Dd / fp32,
+                                     T * ((C + Hd) * 4 + 2 * Hd * Dd * 4 + Hd * Dd * 2) / hbm),
+    }
+    ours, theirs = entry["vifanex"]["prefill_2048_kernels_us"], entry["bizenex"]["prefill_2048_kernels_us"]
+    like = (("hyper_norm", "add_layernorm", "add_layernorm"),
+            ("qkv_full_norm_rope_write", "qk_unit_write", "qk_unit_write"),
+            ("paged_attention", "paged_attention", "paged_attention_bizenex"),
+            ("glu_clamp", "sigmoid_gate", "sigmoid_gate"),
+            ("moe_route", "moe_route", "moe_route_bizenex"),
+            ("moe_experts", "moe_experts", "moe_experts_bizenex"),
+            ("gated_delta", None, None))
+    rows = {}
+    for mine, other, other_ideal in like:
+        a, b = ours.get(mine), theirs.get(other) if other else None
+        if not a:
+            continue
+        rows[mine] = {"us": a["us"], "roofline_us": round(ideal[mine], 1),
+                      "times_roofline": round(a["us"] / ideal[mine], 2)}
+        if b:
+            rows[mine].update({"like": other, "like_us": b["us"],
+                               "like_roofline_us": round(ideal[other_ideal], 1),
+                               "like_times_roofline": round(b["us"] / ideal[other_ideal], 2)})
+    # single tokens at batch 64: the state of every request is read and written once a layer
+    dec = entry["vifanex"].get("decode_b64_kernels_us", {}).get("gated_delta")
+    if dec:
+        state_bytes = n_delta * 64 * 2.0 * Hd * Dd * Dd * 4
+        rows["gated_delta_decode_b64"] = {"us": dec["us"], "roofline_us": round(state_bytes / hbm, 1),
+                                          "times_roofline": round(dec["us"] / (state_bytes / hbm), 2)}
+    return rows
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -1156,14 +1269,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", default="1.2b", choices=sorted(SIZES),
                     help="layer sizes: LFM2-1.2B (the default and the headline), 700M or 350M")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload", "further", "retorax", "bizenex"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload", "further", "retorax", "bizenex", "vifanex"],
                     help="run one part only (for profiling); the JSON line then lacks the rest")
     ap.add_argument("--workloads", default="both", choices=["both", "none"] + sorted(WORKLOADS),
                     help="scheduler workloads to add to the line (default: both)")
     ap.add_argument("--workload", default="350m-mixed", choices=sorted(WORKLOADS),
                     help="with --only workload: which one")
-    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(RETORAX_SIZES),
-                    help="with --only retorax or bizenex: which of the sizes")
+    ap.add_argument("--design-size", default="all", choices=["all"] + sorted(set(RETORAX_SIZES) | set(VIFANEX_SIZES)),
+                    help="with --only retorax, bizenex or vifanex: which of the sizes")
     ap.add_argument("--kernel", default="all",
                     help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK, elementwise, copy_rate or all")
     ap.add_argument("--kernel-batch", type=int, default=64)
@@ -1190,6 +1303,8 @@ def main():
         return run_designs(args)
     if args.only == "bizenex":
         return run_designs(args, "bizenex")
+    if args.only == "vifanex":
+        return run_designs(args, "vifanex")
     if args.only == "workload":
         print(json.dumps({"only": "workload", args.workload: run_workload(args.workload)}))
         return 0

@@ -50,6 +50,7 @@ class CudaOps:
         self.lib.rv_last_error.restype = ctypes.c_char_p
         self.lib.rv_paged_attention_decode_scratch_bytes.restype = c_longlong
         self.lib.rv_gemm_tiled_bytes.restype = c_longlong
+        self.lib.rv_gated_delta_scratch.restype = c_longlong
         self.lib.rv_paged_attention_mixed_scratch_bytes.restype = c_longlong
         self._scratch = {}
         self._retired = []
@@ -1096,16 +1097,18 @@ class CudaOps:
         if state.shape[1] != rec or out.shape[1] != heads * vdim:
             raise KernelError("gated_delta: the record or the output has another size")
         n = proj.shape[0]
-        channels = 2 * kv_heads * dim + heads * vdim
-        prep = torch.empty((n, channels + heads + heads * dim), dtype=torch.float32,
-                           device=proj.device)
+        need = self.lib.rv_gated_delta_scratch(c_int(n), c_int(heads), c_int(kv_heads), c_int(dim),
+                                               c_int(vdim))
+        if need < 0:
+            raise KernelError(f"gated_delta: key heads of {dim} are not supported")
+        scratch = torch.empty((need,), dtype=torch.float32, device=proj.device)
         self._check(self.lib.rv_gated_delta(
             _ptr(proj), c_int(proj.shape[1]), _ptr(lowrank), c_int(lowrank.shape[1]), _ptr(filt),
             _ptr(a_log), _ptr(dt_bias), _ptr(norm_w), _ptr(state), _ptr(ctx.token_req),
-            _ptr(ctx.q_start), _ptr(ctx.state_slot), _ptr(prep), _ptr(out), _code(out.dtype),
+            _ptr(ctx.q_start), _ptr(ctx.state_slot), _ptr(scratch), _ptr(out), _code(out.dtype),
             c_int(n), c_int(ctx.n_reqs), c_int(heads), c_int(kv_heads), c_int(dim), c_int(vdim),
             c_int(taps), c_float(unit_eps), c_float(eps), self._stream()), "gated_delta")
-        self.launches += 1
+        self.launches += 3
 
     # ---- clamped gated activation ----------------------------------------------------------
 
