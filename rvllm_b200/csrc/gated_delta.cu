@@ -12,16 +12,20 @@
 //     times d^(-1/2); beta = sigmoid(proj beta); decay g = exp(-exp(A_log[h]) * softplus(a +
 //     dt_bias)) with a = lowrank[n, h d + i].  Output prep [N, PW] float32, every part a
 //     multiple of four floats so that it can be copied 16 bytes at a time:
-//     q [G, dp] | k [G, dp] | g [H, dp] | v [H dv] | beta [H], where dp >= d is the number of
-//     state rows the scan's threads hold together; rows d .. dp-1 carry q = k = 0, g = 1.
+//     q [G, dp] | k [G, dp] | g [H, dp] | v [H dv] | beta [H] | q.k [G], where dp >= d is the
+//     number of state rows the scan's threads hold together; rows d .. dp-1 carry q = k = 0,
+//     g = 1.
 //   gdr_scan  (one block of 64 threads per (value head, group of value channels, request))
-//     S <- g * S (rows);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  Column j of S
-//     never meets another column, so the columns of a head are spread over blocks; P threads
+//     S <- g * S (rows);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  With S' = g * S
+//     the read-out is o = S'^T q + (q.k) u, so one pass over the rows gives both sums, and the
+//     write k u^T is folded into the next token's pass: a token costs one walk over the state,
+//     not two.  Column j of S never meets another column, so the columns of a head are spread over blocks; P threads
 //     share a column and each keeps R of its rows in registers for the whole portion (P
 //     neighbouring lanes, rows dealt out four at a time, sums by shuffles).  q, k and g of the
-//     coming tokens arrive in a ring of shared-memory slots by asynchronous copies, three
-//     tokens ahead, one barrier a token.  The record's state is read before the first token
-//     and written after the last; o goes out as float32 [N, H dv].
+//     coming tokens (with the block's values and beta) arrive in a ring of shared-memory
+//     slots by asynchronous copies, three tokens ahead, one barrier a token.  The record's
+//     state is read before the first token and written after the last; o goes out as float32
+//     [N, H dv].
 //   gdr_finish  (one block per token, and one per request)
 //     y = o / sqrt(mean_j o^2 + eps) * norm[j] * sigmoid(gate[n, h dv + j]), gate being the
 //     columns lowrank[n, H d + ...]; and the request's convolution inputs move on (the last
@@ -67,13 +71,27 @@ __global__ void gdr_prepare_kernel(const float* __restrict__ proj, int P,
     __syncthreads();
     float* out = prep + (size_t)n * PW;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    for (int head = warp; head < 2 * G; head += nwarps) {  // q heads, then k heads
-        const float* x = act + head * d;
-        float ss = 0.f;
-        for (int i = lane; i < d; i += 32) ss += x[i] * x[i];
-        ss = rv_warp_sum(ss);
-        const float inv = (head < G ? 1.f / sqrtf((float)d) : 1.f) / sqrtf(ss + unit_eps);
-        for (int i = lane; i < dp; i += 32) out[head * dp + i] = i < d ? x[i] * inv : 0.f;
+    float* kq_out = out + (2 * G + H) * dp + ((H * dv + 3) & ~3) + ((H + 3) & ~3);
+    for (int head = warp; head < G; head += nwarps) {      // a query head and its key head
+        const float* xq = act + head * d;
+        const float* xk = act + (G + head) * d;
+        float sq = 0.f, sk = 0.f;
+        for (int i = lane; i < d; i += 32) {
+            sq += xq[i] * xq[i];
+            sk += xk[i] * xk[i];
+        }
+        sq = rv_warp_sum(sq);
+        sk = rv_warp_sum(sk);
+        const float iq = 1.f / sqrtf((float)d) / sqrtf(sq + unit_eps), ik = 1.f / sqrtf(sk + unit_eps);
+        float dot = 0.f;
+        for (int i = lane; i < dp; i += 32) {
+            const float qv = i < d ? xq[i] * iq : 0.f, kv = i < d ? xk[i] * ik : 0.f;
+            out[head * dp + i] = qv;
+            out[(G + head) * dp + i] = kv;
+            dot += qv * kv;
+        }
+        dot = rv_warp_sum(dot);
+        if (lane == 0) kq_out[head] = dot;
     }
     float* gout = out + 2 * G * dp;
     for (int e = threadIdx.x; e < H * dp; e += blockDim.x) {
@@ -95,6 +113,10 @@ __global__ void gdr_prepare_kernel(const float* __restrict__ proj, int P,
 __device__ __forceinline__ void gd_copy16(float* dst, const float* src) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(s), "l"(src) : "memory");
+}
+__device__ __forceinline__ void gd_copy4(float* dst, const float* src) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(src) : "memory");
 }
 __device__ __forceinline__ void gd_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -120,7 +142,8 @@ gdr_scan_kernel(const float* __restrict__ prep, int PW, float* __restrict__ stat
     constexpr int COLS = GD_THREADS / P;
     constexpr int DP = R * P;
     rv_pdl_launch_dependents();
-    extern __shared__ __align__(16) float ring[];          // [GD_STAGES][3][DP]: q | k | g
+    constexpr int SLOT = 3 * DP + ((COLS + 2 + 3) & ~3);   // q | k | g [DP each] | v [COLS] | beta | q.k
+    extern __shared__ __align__(16) float ring[];          // [GD_STAGES][SLOT]
     const int h = blockIdx.x / col_blocks, cb = blockIdx.x - h * col_blocks;
     const int r = blockIdx.y;
     const int slot = state_slot[r];
@@ -131,13 +154,17 @@ gdr_scan_kernel(const float* __restrict__ prep, int PW, float* __restrict__ stat
     const bool live = col < dv;
     const int kvh = h / (H / G);
     const int C = 2 * G * d + H * dv;
-    const int v_off = (2 * G + H) * DP + h * dv + (live ? col : 0);
+    const int v_off = (2 * G + H) * DP + h * dv + cb * COLS;
     const int b_off = (2 * G + H) * DP + ((H * dv + 3) & ~3) + h;
+    const int kq_off = (2 * G + H) * DP + ((H * dv + 3) & ~3) + ((H + 3) & ~3) + kvh;
     rv_pdl_wait();
 
     auto fetch = [&](int t) {
         const float* row = prep + (size_t)(t0 + t) * PW;
-        float* dst = ring + (size_t)(t % GD_STAGES) * 3 * DP;
+        float* dst = ring + (size_t)(t % GD_STAGES) * SLOT;
+        if (tid < COLS && cb * COLS + tid < dv) gd_copy4(dst + 3 * DP + tid, row + v_off + tid);
+        if (tid == GD_THREADS - 1) gd_copy4(dst + 3 * DP + COLS, row + b_off);
+        if (tid == GD_THREADS - 2) gd_copy4(dst + 3 * DP + COLS + 1, row + kq_off);
         for (int e = tid; e < 3 * DP / 4; e += GD_THREADS) {
             const int seg = e / (DP / 4), off = e - seg * (DP / 4);
             const int from = (seg == 0 ? kvh : seg == 1 ? G + kvh : 2 * G + h) * DP;
@@ -149,55 +176,49 @@ gdr_scan_kernel(const float* __restrict__ prep, int PW, float* __restrict__ stat
         gd_commit();
     }
     float* Sg = state + (size_t)slot * rec + (size_t)(taps - 1) * C + (size_t)h * d * dv;
-    float S[R];
+    float S[R], kp[R];                             // state rows; the last token's key, not yet written
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int row = gd_row<P>(i, part);
         S[i] = (live && row < d) ? Sg[(size_t)row * dv + col] : 0.f;
+        kp[i] = 0.f;
     }
-    float v = prep[(size_t)t0 * PW + v_off], beta = prep[(size_t)t0 * PW + b_off];
+    float up = 0.f;                                // the last token's correction
     for (int t = 0; t < qlen; ++t) {
         gd_wait<GD_STAGES - 2>();
         __syncthreads();                           // token t has arrived; slot of t-1 is free
         if (t + GD_STAGES - 1 < qlen) fetch(t + GD_STAGES - 1);
         gd_commit();
-        float v_next = 0.f, beta_next = 0.f;
-        if (t + 1 < qlen) {
-            v_next = prep[(size_t)(t0 + t + 1) * PW + v_off];
-            beta_next = prep[(size_t)(t0 + t + 1) * PW + b_off];
-        }
-        const float4* q4 = reinterpret_cast<const float4*>(ring + (size_t)(t % GD_STAGES) * 3 * DP);
+        const float* slot_t = ring + (size_t)(t % GD_STAGES) * SLOT;
+        const float v = live ? slot_t[3 * DP + tid / P] : 0.f;
+        const float beta = slot_t[3 * DP + COLS], kq = slot_t[3 * DP + COLS + 1];
+        const float4* q4 = reinterpret_cast<const float4*>(slot_t);
         const float4* k4 = q4 + DP / 4;
         const float4* g4 = k4 + DP / 4;
-        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
         for (int i = 0; i < R / 4; ++i) {
-            const float4 kk = k4[i * P + part], gg = g4[i * P + part];
-            S[4 * i + 0] *= gg.x; a0 += S[4 * i + 0] * kk.x;
-            S[4 * i + 1] *= gg.y; a1 += S[4 * i + 1] * kk.y;
-            S[4 * i + 2] *= gg.z; a2 += S[4 * i + 2] * kk.z;
-            S[4 * i + 3] *= gg.w; a3 += S[4 * i + 3] * kk.w;
+            const float4 kk = k4[i * P + part], gg = g4[i * P + part], qq = q4[i * P + part];
+            float s0 = fmaf(kp[4 * i + 0], up, S[4 * i + 0]) * gg.x;
+            float s1 = fmaf(kp[4 * i + 1], up, S[4 * i + 1]) * gg.y;
+            float s2 = fmaf(kp[4 * i + 2], up, S[4 * i + 2]) * gg.z;
+            float s3 = fmaf(kp[4 * i + 3], up, S[4 * i + 3]) * gg.w;
+            S[4 * i + 0] = s0; a0 = fmaf(s0, kk.x, a0); o0 = fmaf(s0, qq.x, o0); kp[4 * i + 0] = kk.x;
+            S[4 * i + 1] = s1; a1 = fmaf(s1, kk.y, a1); o1 = fmaf(s1, qq.y, o1); kp[4 * i + 1] = kk.y;
+            S[4 * i + 2] = s2; a2 = fmaf(s2, kk.z, a2); o2 = fmaf(s2, qq.z, o2); kp[4 * i + 2] = kk.z;
+            S[4 * i + 3] = s3; a3 = fmaf(s3, kk.w, a3); o3 = fmaf(s3, qq.w, o3); kp[4 * i + 3] = kk.w;
         }
-        float acc = (a0 + a1) + (a2 + a3);
+        float acc = (a0 + a1) + (a2 + a3), o = (o0 + o1) + (o2 + o3);
 #pragma unroll
-        for (int o = P / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-        const float u = beta * (v - acc);
-        a0 = a1 = a2 = a3 = 0.f;
-#pragma unroll
-        for (int i = 0; i < R / 4; ++i) {
-            const float4 kk = k4[i * P + part], qq = q4[i * P + part];
-            S[4 * i + 0] += kk.x * u; a0 += S[4 * i + 0] * qq.x;
-            S[4 * i + 1] += kk.y * u; a1 += S[4 * i + 1] * qq.y;
-            S[4 * i + 2] += kk.z * u; a2 += S[4 * i + 2] * qq.z;
-            S[4 * i + 3] += kk.w * u; a3 += S[4 * i + 3] * qq.w;
+        for (int s = P / 2; s > 0; s >>= 1) {
+            acc += __shfl_xor_sync(0xffffffffu, acc, s);
+            o += __shfl_xor_sync(0xffffffffu, o, s);
         }
-        float o = (a0 + a1) + (a2 + a3);
-#pragma unroll
-        for (int s = P / 2; s > 0; s >>= 1) o += __shfl_xor_sync(0xffffffffu, o, s);
-        if (live && part == 0) o_out[(size_t)(t0 + t) * H * dv + h * dv + col] = o;
-        v = v_next;
-        beta = beta_next;
+        up = beta * (v - acc);
+        if (live && part == 0) o_out[(size_t)(t0 + t) * H * dv + h * dv + col] = fmaf(kq, up, o);
     }
+#pragma unroll
+    for (int i = 0; i < R; ++i) S[i] = fmaf(kp[i], up, S[i]);
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int row = gd_row<P>(i, part);
@@ -272,7 +293,7 @@ static bool gd_shape(int d, int* R, int* P) {
 extern "C" long long rv_gated_delta_scratch(int n_tokens, int H, int G, int d, int dv) {
     int R = 0, P = 0;
     if (!gd_shape(d, &R, &P)) return -1;
-    const long long pw = (long long)(2 * G + H) * R * P + gd_pad4(H * dv) + gd_pad4(H);
+    const long long pw = (long long)(2 * G + H) * R * P + gd_pad4(H * dv) + gd_pad4(H) + gd_pad4(G);
     return (long long)n_tokens * (pw + (long long)H * dv);
 }
 
@@ -282,7 +303,9 @@ static void gd_launch_scan(const float* prep, int PW, float* state, long long re
                            int taps, cudaStream_t s) {
     const int cols = GD_THREADS / P;
     const int col_blocks = (dv + cols - 1) / cols;
-    const size_t smem = (size_t)GD_STAGES * 3 * R * P * sizeof(float);
+    const size_t smem = (size_t)GD_STAGES * (3 * R * P + ((cols + 2 + 3) & ~3)) * sizeof(float);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(gdr_scan_kernel<R, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     rv_launch(gdr_scan_kernel<R, P>, dim3(H * col_blocks, n_reqs), dim3(GD_THREADS), smem, s, prep, PW,
               state, rec, q_start, state_slot, o, H, G, d, dv, taps, col_blocks);
 }
@@ -306,7 +329,7 @@ extern "C" int rv_gated_delta(const float* proj, int P, const float* lowrank, in
         RV_FAIL("gated_delta: key heads of %d are not supported (at most 1024)", d);
     if (n_reqs > 65535) RV_FAIL("gated_delta: batch too large");
     const int dp = R * TP;
-    const int PW = (2 * G + H) * dp + gd_pad4(H * dv) + gd_pad4(H);
+    const int PW = (2 * G + H) * dp + gd_pad4(H * dv) + gd_pad4(H) + gd_pad4(G);
     const long long rec = rv_gated_delta_record(H, G, d, dv, taps);
     const size_t smem1 = (size_t)C * sizeof(float);
     if (smem1 > 200 * 1024) RV_FAIL("gated_delta: %d channels do not fit shared memory", C);

@@ -538,7 +538,8 @@ def test_window_edges_with_a_standout_key(ops, dtype, sizes, window):
                 continue
             kk = k.clone()
             for a in range(G):                            # this key answers every head of its group
-                kk[target, a] = q[p, a * (H // G):(a + 1) * (H // G)].mean(0) * 6.0
+                m = q[p, a * (H // G):(a + 1) * (H // G)].mean(0)
+                kk[target, a] = m * (24.0 / (scale * float(m @ m)))     # a score of 24
             kk = kk.to(dtype).double()
             want = plain_window_attend(q[first:first + T].numpy(), kk[:p + 1].numpy(), v[:p + 1].numpy(),
                                        scale, window, first)
