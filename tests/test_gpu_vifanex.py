@@ -305,13 +305,14 @@ def test_gated_delta_against_plain(ops, dtype, sizes):
     want = [plain_delta(p.numpy(), l.numpy(), filt.numpy(), a_log.numpy(), dt_bias.numpy(),
                         norm_w.numpy(), H, G, d, dv, eps) for p, l in seqs]
     C = 2 * G * d + H * dv
-    for cuts in ((64,), (1,), (7, 2, 1, 1, 5, 3, 2), (taps, 1, taps + 1)):
+    # (2, 1, 1): as many tokens as requests, one request without any, so one has two
+    for cuts in ((64,), (1,), (7, 2, 1, 1, 5, 3, 2), (taps, 1, taps + 1), (2, 1, 1)):
         slots = [5, 2, 3]
         got, state = run_delta(ops, seqs, cuts, H, G, d, dv, taps, filt, a_log, dt_bias, norm_w, eps,
                                dtype, slots)
         for i in range(3):
             close(got[i], want[i][0], dtype)
-            S = state[slots[i], (taps - 1) * C:].reshape(H, d, dv)
+            S = state[slots[i], (taps - 1) * C:].reshape(H, dv, d).transpose(1, 2)   # a column's rows lie together
             close(S, want[i][1], torch.float32, scale=max(1.0, float(np.abs(want[i][1]).max())))
             # the record's first part: the last taps-1 inputs, oldest first, zeros before the start
             T = seqs[i][0].shape[0]
@@ -358,7 +359,7 @@ def test_gated_delta_order_within_a_token(ops):
     got, state = run_delta(ops, [(proj, low)], (1,), H, G, d, dv, taps, filt, a_log, dt_bias, norm_w, 1e-5,
                            torch.float32, [0])
     close(got[0], want, torch.float32)
-    close(state[0].reshape(H, d, dv), S, torch.float32)
+    close(state[0].reshape(H, dv, d).transpose(1, 2), S, torch.float32)
 
 
 # ---- the clamped gated feed-forward and the mixture -------------------------------------------
