@@ -1002,6 +1002,8 @@ def run_designs(args, which="retorax"):
     out = {"only": which, "peaks": pk["source"], "fp32_tflops_nominal": round(FP32_TFLOPS_NOMINAL, 1)}
     gen = torch.Generator().manual_seed(0)
     T, CTX = 2048, 1024
+    sampler = ClockSampler()
+    sampler.start()
     sizes = {"retorax": RETORAX_SIZES, "bizenex": BIZENEX_SIZES, "vifanex": VIFANEX_SIZES}[which]
     for size_name, sz in sizes.items():
         if args.design_size not in ("all", size_name):
@@ -1085,6 +1087,7 @@ def run_designs(args, which="retorax"):
         entry["rooflines"] = {"retorax": design_rooflines, "bizenex": bizenex_rooflines,
                               "vifanex": vifanex_rooflines}[which](sz, entry, pk, T, CTX)
         out[size_name] = entry
+    out["clocks"] = sampler.stop()
     print(json.dumps(out))
     return 0
 
