@@ -49,20 +49,51 @@ __global__ void qkv_full_kernel(const float* __restrict__ rows, const float* __r
     sk = rv_block_sum(sk, red);
     // without norm weights the projections stay as they are
     const float dq = wq ? sqrtf(sq / (float)Q + eps) : 1.f, dk = wk ? sqrtf(sk / (float)K + eps) : 1.f;
-    for (int e = threadIdx.x; e < Q + K; e += blockDim.x) {
-        const bool is_q = e < Q;
-        const int j = (is_q ? e : e - Q) % d;             // place in its head
-        const float den = is_q ? dq : dk;
-        const float* w = is_q ? wq : (wk ? wk - Q : nullptr);
-        float val = w ? qk[e] / den * w[e] : qk[e];
-        if (j < rot_dims) {
-            const float other = w ? qk[e ^ 1] / den * w[e ^ 1] : qk[e ^ 1];   // heads start at even places
-            const float ang = (float)pos * freq[j >> 1];
-            const float c = cosf(ang), s = sinf(ang);
-            val = (j & 1) ? val * c + other * s : val * c - other * s;
+    if ((d & 1) == 0) {
+        // heads of even size: a thread takes a pair (2i, 2i + 1), so one division by the head
+        // size, one sine and one cosine serve two values
+        for (int p = threadIdx.x; p < (Q + K) / 2; p += blockDim.x) {
+            const int e = 2 * p;
+            const bool is_q = e < Q;
+            const int j = (is_q ? e : e - Q) % d;             // place in its head, even
+            const float den = is_q ? dq : dk;
+            const float* w = is_q ? wq : (wk ? wk - Q : nullptr);
+            float a = qk[e], b = qk[e + 1];
+            if (w) {
+                a = a / den * w[e];
+                b = b / den * w[e + 1];
+            }
+            if (j < rot_dims) {
+                const float ang = (float)pos * freq[j >> 1];
+                const float c = cosf(ang), sn = sinf(ang);
+                const float ra = a * c - b * sn, rb = b * c + a * sn;
+                a = ra;
+                b = rb;
+            }
+            if (is_q) {
+                rv_store(q_out + (size_t)n * Q + e, a);
+                rv_store(q_out + (size_t)n * Q + e + 1, b);
+            } else if (slot >= 0) {
+                rv_store(k_cache + (size_t)slot * K + (e - Q), a);
+                rv_store(k_cache + (size_t)slot * K + (e - Q) + 1, b);
+            }
         }
-        if (is_q) rv_store(q_out + (size_t)n * Q + e, val);
-        else if (slot >= 0) rv_store(k_cache + (size_t)slot * K + (e - Q), val);
+    } else {
+        for (int e = threadIdx.x; e < Q + K; e += blockDim.x) {
+            const bool is_q = e < Q;
+            const int j = (is_q ? e : e - Q) % d;             // place in its head
+            const float den = is_q ? dq : dk;
+            const float* w = is_q ? wq : (wk ? wk - Q : nullptr);
+            float val = w ? qk[e] / den * w[e] : qk[e];
+            if (j < rot_dims) {
+                const float other = w ? qk[e ^ 1] / den * w[e ^ 1] : qk[e ^ 1];   // heads start at even places
+                const float ang = (float)pos * freq[j >> 1];
+                const float c = cosf(ang), s = sinf(ang);
+                val = (j & 1) ? val * c + other * s : val * c - other * s;
+            }
+            if (is_q) rv_store(q_out + (size_t)n * Q + e, val);
+            else if (slot >= 0) rv_store(k_cache + (size_t)slot * K + (e - Q), val);
+        }
     }
     for (int e = threadIdx.x; e < V; e += blockDim.x) {
         float val = row[Q + K + e] + (bias ? bias[Q + K + e] : 0.f);
