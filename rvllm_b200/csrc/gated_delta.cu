@@ -16,20 +16,31 @@
 //     q [G, dp] | k [G, dp] | g [H, dp] | v [H dv] | beta [H] | q.k [G], where dp >= d is the
 //     number of state rows the scan's threads hold together; rows d .. dp-1 carry q = k = 0,
 //     g = 1.
-//   gdr_scan  (one block of up to 128 threads per (value head, group of value channels, request))
-//     S <- g * S (rows);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  With S' = g * S
-//     the read-out is o = S'^T q + (q.k) u, so one pass over the rows gives both sums, and the
-//     write k u^T is folded into the next token's pass: a token costs one walk over the state,
-//     not two.  Column j of S never meets another column, so the columns of a head are spread
-//     over blocks; P threads share a column and each keeps R of its rows in registers for the
-//     whole portion (P neighbouring lanes, rows dealt out four at a time, sums by shuffles).  A
-//     token is one step of a dependent chain, so R is small (8 up to key size 256): a warp
-//     issues few instructions per token and a head's work is spread over many warps.  q, k
-//     and g of the tokens (with the block's values and beta) arrive sixteen tokens at a time
-//     in one of two shared-memory buffers by asynchronous copies, the next sixteen while these
-//     are worked on: two barriers per sixteen tokens, none between tokens.  The record's
-//     state is read before the first token and written after the last; o goes out as float32
-//     [N, H dv].
+//   gdr_scan  (one block per (value head, group of value channels, request): up to 128 working
+//   threads and a warp that brings the inputs)
+//     S <- g * S (rows);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  Column j of S
+//     never meets another column, so the columns of a head are spread over blocks; P threads
+//     share a column and each keeps R of its rows in registers for the whole portion (P
+//     neighbouring lanes, rows dealt out four at a time, sums by shuffles).  A token is one step
+//     of a dependent chain, so R is small (8 up to key size 256): a warp issues few
+//     instructions per token and a head's work is spread over many warps.
+//     The rows lag two writes behind: after token t the state is Z + a u' + k_t u, with u' and u
+//     the corrections of tokens t-1 and t and a = k_{t-1} * g_t.  Then Z_t = (Z + a u'') * g_t
+//     needs only the correction before last, and u' enters the token's sums through
+//     kk = sum_i k_{t-1}[i] g_t[i] k_t[i] and kq = sum_i k_{t-1}[i] g_t[i] q_t[i]:
+//     S_t^T k_t = Z_t^T k_t + u' kk,  o = Z_t^T q_t + u' kq + u (q_t . k_t).  One pass over the
+//     rows gives both sums of a token, and two tokens' passes and shuffles are independent, so
+//     tokens are worked in pairs.  At a portion's end the two writes are added and the record
+//     holds the state itself.
+//     q, k and g of the tokens (with the block's values, beta and q.k) arrive sixteen tokens
+//     at a time in one of three shared-memory buffers by asynchronous copies of the bringing
+//     warp, two chunks ahead; that warp also forms kk and kq of the chunk that has arrived.
+//     One barrier per sixteen tokens, none between tokens.  The record's state is read before
+//     the first token and written after the last; o goes out as float32 [N, H dv].
+//   gdr_single  (a step in which every request brings one token; same grid, no bringing warp)
+//     the same update without the lag: every thread copies its share of the token, reads its
+//     rows meanwhile, and writes them back with the write added.  Small blocks, so that many
+//     fit a multiprocessor: the step is bound by reading and writing every state once.
 //   gdr_finish  (one block per token, and one per request)
 //     y = o / sqrt(mean_j o^2 + eps) * norm[j] * sigmoid(gate[n, h dv + j]), gate being the
 //     columns lowrank[n, H d + ...]; and the request's convolution inputs move on (the last
@@ -133,7 +144,7 @@ __device__ __forceinline__ void gd_wait() {
 #define GD_MAX_THREADS 128      // working threads of a scan block
 #define GD_SINGLE_THREADS 128   // threads of a single-token block
 #define GD_CHUNK 16             // tokens that arrive together
-#define GD_BUFFER_FLOATS 8192    // one of the two buffers holds at most this much
+#define GD_BUFFER_FLOATS 8192   // one of the three buffers holds at most this much
 
 // Row of the state that register r of the thread with number `part` among the P of a column
 // holds: rows are dealt out four at a time, so that the P threads read neighbouring float4s.
