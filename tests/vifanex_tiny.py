@@ -114,7 +114,7 @@ VF_D = {
          "mlp": _moe(128, 2.0, 8, 2, (4, 2), 1.5, (64, 2.0))},
         {"type": "channel_delta", "mixer": _delta(4, 2, 64, 64, 4, 16, 16), "mlp": _dense(256, 1.0)},
         {"type": "attention", "mixer": _attn(12, 2, 32, 32, 0.2, 17, (32, 5000.0, None)),
-         "mlp": _moe(64, 1.0, 16, 4, (4, 3), 1.0)},
+         "mlp": _moe(64, 1.0, 16, 5, (8, 3), 1.0)},
         {"type": "attention", "mixer": _attn(4, 2, 64, 64, 0.125, 64, (64, 10000.0, None), True),
          "mlp": None},
         {"type": "channel_delta", "mixer": _delta(8, 2, 32, 32, 4, 8, 32),
