@@ -29,19 +29,20 @@ import numpy as np
 import torch
 
 from ..errors import CacheError
-from ..parts.base import PagedNeed, StateNeed
+from ..parts.base import PagedNeed, SeveralNeeds, StateNeed
 from .pages import PagePool
 
 
 @dataclass
 class CacheView:
     """What one call of the run order sees of the cache."""
-    kind: str                          # "paged" or "state"
+    kind: str                          # "paged", "state" or "several"
     owns: bool                         # False: reads the cache another call writes
     group: int = -1                    # paged: index into StepContext.groups
     k: Optional[torch.Tensor] = None   # paged: [pages, page_size, kv_heads, head_dim]
     v: Optional[torch.Tensor] = None
     state: Optional[torch.Tensor] = None   # state: float32 [slots, *shape]
+    parts: Optional[list] = None       # several: one view (or None) per branch of the mixer
 
 
 @dataclass
@@ -108,7 +109,8 @@ class CacheManager:
     def __init__(self, needs: Sequence[Optional[object]], cache_of: Sequence[Optional[int]],
                  page_size: int, num_pages: int, max_requests: int,
                  dtype: torch.dtype = torch.float32, device="cpu", allocate: bool = True):
-        """needs[i]: PagedNeed, StateNeed or None for call i of the run order;
+        """needs[i]: PagedNeed, StateNeed, SeveralNeeds (a mixer of several mixers: each part is
+        handled as a call of its own, named (i, part)) or None for call i of the run order;
         cache_of[i]: the call whose cache call i reads, or None.  `num_pages` pages per
         group; `max_requests` state slots.  `allocate=False` keeps only the
         bookkeeping (for tests and planning)."""
@@ -126,7 +128,15 @@ class CacheManager:
         self._views: List[Optional[CacheView]] = [None] * len(needs)
         call_group: Dict[int, int] = {}
         state_calls: Dict[tuple, List[int]] = {}
+        flat = []
         for i, need in enumerate(needs):
+            if isinstance(need, SeveralNeeds):
+                if cache_of[i] is not None:
+                    raise CacheError(f"call {i}: a mixer of several mixers keeps its own caches")
+                flat += [((i, j), part) for j, part in enumerate(need.parts)]
+            else:
+                flat.append((i, need))
+        for i, need in flat:
             if isinstance(need, PagedNeed):
                 gi = next((g for g, grp in enumerate(self.groups) if grp.need == need), None)
                 if gi is None:
@@ -154,17 +164,23 @@ class CacheManager:
                 shape = (len(grp.calls), num_pages, page_size, grp.need.num_kv_heads)
                 grp.k = torch.zeros(shape + (grp.need.head_dim,), dtype=dtype, device=device)
                 grp.v = torch.zeros(shape + (grp.need.value_dim,), dtype=dtype, device=device)
-        for i, need in enumerate(needs):
-            src = cache_of[i] if cache_of[i] is not None else i
-            owns = cache_of[i] is None
+        def view(src, owns):
             if src in call_group:
                 grp = self.groups[call_group[src]]
                 ci = grp.calls.index(src)
-                self._views[i] = CacheView("paged", owns, call_group[src],
-                                           grp.k[ci] if allocate else None,
-                                           grp.v[ci] if allocate else None)
-            elif src in self.states:
-                self._views[i] = CacheView("state", owns, state=self.states[src])
+                return CacheView("paged", owns, call_group[src], grp.k[ci] if allocate else None,
+                                 grp.v[ci] if allocate else None)
+            if src in self.states:
+                return CacheView("state", owns, state=self.states[src])
+            return None
+
+        for i, need in enumerate(needs):
+            if isinstance(need, SeveralNeeds):
+                self._views[i] = CacheView("several", True,
+                                           parts=[view((i, j), True) for j in range(len(need.parts))])
+                continue
+            self._views[i] = view(cache_of[i] if cache_of[i] is not None else i,
+                                  cache_of[i] is None)
 
     # ---- what the model sees ---------------------------------------------------------
 

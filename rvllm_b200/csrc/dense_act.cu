@@ -2,6 +2,7 @@
 //   xIELU with two learned numbers p, q:
 //     z > 0 :  softplus(p) z^2 + z/2
 //     z <= 0:  (1/2 + softplus(q)) (e^z - 1 - z) + z/2
+//   relu squared: max(z, 0)^2 (at the end of the file).
 // Arithmetic in float32 whatever the storage type.  Plain reference: tests/plain_ops.py xielu.
 #include "common.cuh"
 
@@ -117,5 +118,59 @@ extern "C" int rv_glu_clamp(const void* in, const float* bias, void* out, int dt
                       (rv_launch(glu_clamp_kernel<T>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
                                  (const T*)in, bias, (T*)out, total, F, limit, alpha)));
     RV_CHECK_LAUNCH("glu_clamp");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// The square of relu: out = max(z, 0)^2.  Arithmetic in float32.  Plain reference:
+// tests/plain_ops.py relu2.
+template <typename T>
+__global__ void relu2_kernel(const T* __restrict__ in, T* __restrict__ out, size_t total) {
+    rv_pdl_prologue();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const float z = fmaxf(rv_load(in + i), 0.f);
+        rv_store(out + i, z * z);
+    }
+}
+
+// bfloat16, eight values per 16-byte access
+__global__ void relu2_bf16x8_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                    size_t total8) {
+    rv_pdl_prologue();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 raw = in[i];
+        uint4 o4;
+        const __nv_bfloat162* x2 = (const __nv_bfloat162*)&raw;
+        __nv_bfloat162* o2 = (__nv_bfloat162*)&o4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 z = __bfloat1622float2(x2[k]);
+            z.x = fmaxf(z.x, 0.f);
+            z.y = fmaxf(z.y, 0.f);
+            o2[k] = __floats2bfloat162_rn(z.x * z.x, z.y * z.y);
+        }
+        out[i] = o4;
+    }
+}
+
+extern "C" int rv_relu2(const void* in, void* out, int dtype, int n_rows, int width, void* stream) {
+    if (n_rows == 0) return 0;
+    if (n_rows < 0 || width <= 0) RV_FAIL("relu2: bad sizes");
+    const size_t total = (size_t)n_rows * width;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RV_DTYPE_BF16 && total % 8 == 0 && (uintptr_t)in % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const size_t total8 = total / 8;
+        const int blocks = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
+        rv_launch(relu2_bf16x8_kernel, dim3(blocks), dim3(256), 0, s, (const uint4*)in, (uint4*)out,
+                  total8);
+    } else {
+        const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+        RV_DISPATCH_DTYPE(dtype, "relu2",
+                          (rv_launch(relu2_kernel<T>, dim3(blocks), dim3(256), 0, s, (const T*)in,
+                                     (T*)out, total)));
+    }
+    RV_CHECK_LAUNCH("relu2");
     return 0;
 }

@@ -74,7 +74,8 @@ extern "C" int rv_embed(const void* table, int dtype, const int* ids, float* out
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                    const float* __restrict__ weight, TO* __restrict__ out,
-                                   const int* __restrict__ rows, int hidden, float eps) {
+                                   const int* __restrict__ rows, int hidden, float eps,
+                                   const float* __restrict__ dscale, const float* __restrict__ add) {
     rv_pdl_prologue();
     extern __shared__ float row[];
     __shared__ float scratch[33];
@@ -83,8 +84,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     float ss = 0.f;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float x = resid ? resid[in + i] : 0.f;
-        if (delta) x += rv_load(delta + in + i);
-        if (!rows && delta && resid) resid[in + i] = x;
+        if (delta) x += dscale ? dscale[i] * rv_load(delta + in + i) : rv_load(delta + in + i);
+        if (add) x += add[i];
+        if (!rows && (delta || add) && resid) resid[in + i] = x;
         row[i] = x;
         ss += x * x;
     }
@@ -100,7 +102,9 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
 template <typename TD, typename TO, int CHUNKS>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
                                        const float* __restrict__ weight, TO* __restrict__ out,
-                                       const int* __restrict__ rows, int hidden, float eps) {
+                                       const int* __restrict__ rows, int hidden, float eps,
+                                       const float* __restrict__ dscale,
+                                       const float* __restrict__ add) {
     rv_pdl_prologue();
     __shared__ float scratch[33];
     const int m = blockIdx.x;
@@ -115,10 +119,18 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
             x[c] = resid ? rv_load4(resid + in + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
             w[c] = rv_load4(weight + 4 * i);
             if (delta) {
-                const float4 d = rv_load4(delta + in + 4 * i);
+                float4 d = rv_load4(delta + in + 4 * i);
+                if (dscale) {
+                    const float4 g = rv_load4(dscale + 4 * i);
+                    d.x *= g.x; d.y *= g.y; d.z *= g.z; d.w *= g.w;
+                }
                 x[c].x += d.x; x[c].y += d.y; x[c].z += d.z; x[c].w += d.w;
-                if (!rows && resid) rv_store4(resid + in + 4 * i, x[c]);
             }
+            if (add) {
+                const float4 a = rv_load4(add + 4 * i);
+                x[c].x += a.x; x[c].y += a.y; x[c].z += a.z; x[c].w += a.w;
+            }
+            if ((delta || add) && !rows && resid) rv_store4(resid + in + 4 * i, x[c]);
             ss += x[c].x * x[c].x + x[c].y * x[c].y + x[c].z * x[c].z + x[c].w * x[c].w;
         }
     }
@@ -137,9 +149,10 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ resid, const TD* __re
 template <typename TD, typename TO>
 static int add_rmsnorm_launch(float* resid, const void* delta, const float* weight, void* out,
                               const int* rows, int n_rows, int hidden, float eps,
-                              cudaStream_t stream) {
+                              const float* dscale, const float* add, cudaStream_t stream) {
     const bool aligned = ((uintptr_t)resid % 16 == 0) && ((uintptr_t)weight % 16 == 0) &&
-                         ((uintptr_t)out % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0);
+                         ((uintptr_t)out % 16 == 0) && (!delta || (uintptr_t)delta % 16 == 0) &&
+                         ((uintptr_t)dscale % 16 == 0) && ((uintptr_t)add % 16 == 0);
     if (hidden % 4 == 0 && hidden <= 16384 && aligned) {
         const int nvec = hidden / 4;
         int threads = ((nvec + 31) / 32) * 32;
@@ -150,13 +163,13 @@ static int add_rmsnorm_launch(float* resid, const void* delta, const float* weig
         }
         if (chunks == 1)
             rv_launch(add_rmsnorm_vec_kernel<TD, TO, 1>, dim3(n_rows), dim3(threads), 0, stream, 
-                resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps);
+                resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, dscale, add);
         else if (chunks == 2)
             rv_launch(add_rmsnorm_vec_kernel<TD, TO, 2>, dim3(n_rows), dim3(threads), 0, stream, 
-                resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps);
+                resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, dscale, add);
         else
             rv_launch(add_rmsnorm_vec_kernel<TD, TO, 4>, dim3(n_rows), dim3(threads), 0, stream, 
-                resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps);
+                resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, dscale, add);
         RV_CHECK_LAUNCH("add_rmsnorm");
         return 0;
     }
@@ -169,30 +182,68 @@ static int add_rmsnorm_launch(float* resid, const void* delta, const float* weig
     }
     const int threads = hidden >= 1024 ? 256 : 128;
     rv_launch(add_rmsnorm_kernel<TD, TO>, dim3(n_rows), dim3(threads), smem, stream, 
-        resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps);
+        resid, (const TD*)delta, weight, (TO*)out, rows, hidden, eps, dscale, add);
     RV_CHECK_LAUNCH("add_rmsnorm");
     return 0;
+}
+
+// `dscale` float32 [hidden], if given, multiplies the pending rows channel by channel before they
+// are added (a layer's scale on its sub-layer's output); `add` float32 [hidden], if given, is one
+// vector added to every row of the stream (what a repeated stretch of layers adds before a pass).
+extern "C" int rv_add_rmsnorm_ex(float* resid, const void* delta, int delta_dtype,
+                                 const float* weight, void* out, int out_dtype, const int* rows,
+                                 int n_rows, int hidden, float eps, const float* dscale,
+                                 const float* add, void* stream) {
+    if (n_rows == 0) return 0;
+    if (n_rows < 0 || hidden <= 0) RV_FAIL("add_rmsnorm: bad sizes");
+    if (!resid && !delta) RV_FAIL("add_rmsnorm: neither a stream nor rows to normalise");
+    if (dscale && !delta) RV_FAIL("add_rmsnorm: a scale without rows to scale");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (delta_dtype == RV_DTYPE_F32 && out_dtype == RV_DTYPE_F32)
+        return add_rmsnorm_launch<float, float>(resid, delta, weight, out, rows, n_rows, hidden, eps,
+                                                dscale, add, s);
+    if (delta_dtype == RV_DTYPE_BF16 && out_dtype == RV_DTYPE_BF16)
+        return add_rmsnorm_launch<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, rows,
+                                                                 n_rows, hidden, eps, dscale, add, s);
+    if (delta_dtype == RV_DTYPE_F32 && out_dtype == RV_DTYPE_BF16)
+        return add_rmsnorm_launch<float, __nv_bfloat16>(resid, delta, weight, out, rows, n_rows,
+                                                        hidden, eps, dscale, add, s);
+    if (delta_dtype == RV_DTYPE_BF16 && out_dtype == RV_DTYPE_F32)
+        return add_rmsnorm_launch<__nv_bfloat16, float>(resid, delta, weight, out, rows, n_rows,
+                                                        hidden, eps, dscale, add, s);
+    RV_FAIL("add_rmsnorm: unknown dtype codes %d, %d", delta_dtype, out_dtype);
 }
 
 extern "C" int rv_add_rmsnorm(float* resid, const void* delta, int delta_dtype, const float* weight,
                               void* out, int out_dtype, const int* rows, int n_rows, int hidden,
                               float eps, void* stream) {
-    if (n_rows == 0) return 0;
-    if (n_rows < 0 || hidden <= 0) RV_FAIL("add_rmsnorm: bad sizes");
-    if (!resid && !delta) RV_FAIL("add_rmsnorm: neither a stream nor rows to normalise");
-    cudaStream_t s = (cudaStream_t)stream;
-    if (delta_dtype == RV_DTYPE_F32 && out_dtype == RV_DTYPE_F32)
-        return add_rmsnorm_launch<float, float>(resid, delta, weight, out, rows, n_rows, hidden, eps, s);
-    if (delta_dtype == RV_DTYPE_BF16 && out_dtype == RV_DTYPE_BF16)
-        return add_rmsnorm_launch<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, out, rows,
-                                                                 n_rows, hidden, eps, s);
-    if (delta_dtype == RV_DTYPE_F32 && out_dtype == RV_DTYPE_BF16)
-        return add_rmsnorm_launch<float, __nv_bfloat16>(resid, delta, weight, out, rows, n_rows,
-                                                        hidden, eps, s);
-    if (delta_dtype == RV_DTYPE_BF16 && out_dtype == RV_DTYPE_F32)
-        return add_rmsnorm_launch<__nv_bfloat16, float>(resid, delta, weight, out, rows, n_rows,
-                                                        hidden, eps, s);
-    RV_FAIL("add_rmsnorm: unknown dtype codes %d, %d", delta_dtype, out_dtype);
+    return rv_add_rmsnorm_ex(resid, delta, delta_dtype, weight, out, out_dtype, rows, n_rows, hidden,
+                             eps, nullptr, nullptr, stream);
+}
+
+// `out[i] = sa * a[i] + sb * b[i]`: the sum of two mixers that read the same input, each with its
+// factor.  float32 arithmetic, rounded once.
+template <typename T>
+__global__ void weighted_sum_kernel(const T* __restrict__ a, float sa, const T* __restrict__ b,
+                                    float sb, T* __restrict__ out, size_t total) {
+    rv_pdl_prologue();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (size_t)gridDim.x * blockDim.x)
+        rv_store(out + i, sa * rv_load(a + i) + sb * rv_load(b + i));
+}
+
+extern "C" int rv_weighted_sum(const void* a, float sa, const void* b, float sb, void* out,
+                               int dtype, long long total, void* stream) {
+    if (total == 0) return 0;
+    if (total < 0 || !a || !b || !out) RV_FAIL("weighted_sum: bad arguments");
+    const long long want = (total + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    RV_DISPATCH_DTYPE(dtype, "weighted_sum",
+                      (rv_launch(weighted_sum_kernel<T>, dim3(blocks), dim3(256), 0,
+                                 (cudaStream_t)stream, (const T*)a, sa, (const T*)b, sb, (T*)out,
+                                 (size_t)total)));
+    RV_CHECK_LAUNCH("weighted_sum");
+    return 0;
 }
 
 // ---------------------------------------------------------------------------------

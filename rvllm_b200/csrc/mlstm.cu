@@ -1,0 +1,242 @@
+// The matrix memory with exponential gates (mLSTM): per head a float32 matrix C [d, dv], a
+// vector n [d] and a running maximum m (0 at the start) that keeps the exponentials in range.
+// For a token with log input gate li and log forget gate lf:
+//
+//     m'  = max(lf + m, li);   a = exp(lf + m - m');   b = exp(li - m')
+//     C  <- a C + b k v^T;     n <- a n + b k;          m <- m'
+//     o   = C^T q / (max(|n . q|, exp(-m)) + 1e-6)
+//     y   = o / sqrt(mean(o^2) + eps) * w * sigmoid(g)                      per head
+//
+// with li = cap tanh((i + bi) / cap), lf = logsigmoid(cap tanh((f + bf) / cap)) and q scaled
+// by d^(-1/2).  Everything here is float32.  n is kept as one more column of C whose value is
+// always 1, so that n . q comes out of the same pass as C^T q.
+//
+// rows [N, stride] float32: q [H d] | k [H d] | v [H dv] | i [H] | f [H] | g [H dv].
+// A request's record [H (dv + 1) d + H]: per head the dv + 1 columns, a column's d rows side by
+// side; then the H maxima.  Three launches for any mixture of portions and single tokens:
+//
+//   gates   block per (request, head): li and lf of all the request's tokens in parallel, the
+//           maxima one after another by one thread (an add and a max a token), then a, b and
+//           exp(-m) of all tokens in parallel -> gate [N, H, 4]; the record's maximum moves on.
+//   scan    block per (tile of columns, head, request): P neighbouring lanes share a column and
+//           each holds R of its rows in registers for the whole portion; q, k, v and the gates
+//           of sixteen tokens at a time are staged in shared memory; per token every lane does
+//           R multiply-adds into its rows and R into its part of the column's sum, which P
+//           lanes add by shuffles -> num [N, H, dv + 1].  A column never meets another, so the
+//           columns of a head are spread over blocks, and a token's sums are formed in the same
+//           order however its prompt was cut.
+//   finish  warp per (token, head): the division, the head's norm, weight and gate.
+// Plain reference: tests/plain_ops.py mlstm.
+#include "common.cuh"
+
+#define ML_TC 16            // tokens staged at a time
+#define ML_THREADS 128
+
+__device__ __forceinline__ float ml_logsigmoid(float z) {
+    return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+}
+
+__global__ void __launch_bounds__(ML_THREADS) mlstm_gates_kernel(
+    const float* __restrict__ rows, int stride, int i_off, int f_off, const float* __restrict__ bi,
+    const float* __restrict__ bf, float cap, const int* __restrict__ q_start,
+    const int* __restrict__ state_slot, float* __restrict__ state, long long rec, int m_off,
+    float* __restrict__ gate, int H) {
+    rv_pdl_launch_dependents();
+    const int r = blockIdx.x, h = blockIdx.y;
+    const int slot = state_slot[r];
+    const int a0 = q_start[r], a1 = q_start[r + 1];
+    const float b_i = bi[h], b_f = bf[h];
+    rv_pdl_wait();
+    if (slot < 0 || a1 <= a0) return;
+    constexpr int CH = 1024;
+    __shared__ float li[CH], lf[CH], ms[CH + 1];
+    float* m_rec = state + (size_t)slot * rec + m_off + h;
+    if (threadIdx.x == 0) ms[0] = *m_rec;
+    for (int c0 = a0; c0 < a1; c0 += CH) {
+        const int n = min(CH, a1 - c0);
+        for (int t = threadIdx.x; t < n; t += blockDim.x) {
+            const float* row = rows + (size_t)(c0 + t) * stride;
+            li[t] = cap * tanhf((row[i_off + h] + b_i) / cap);
+            lf[t] = ml_logsigmoid(cap * tanhf((row[f_off + h] + b_f) / cap));
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = ms[0];
+            for (int t = 0; t < n; ++t) {
+                m = fmaxf(lf[t] + m, li[t]);
+                ms[t + 1] = m;
+            }
+        }
+        __syncthreads();
+        for (int t = threadIdx.x; t < n; t += blockDim.x) {
+            const float m_old = ms[t], m_new = ms[t + 1];
+            *(float4*)(gate + ((size_t)(c0 + t) * H + h) * 4) =
+                make_float4(expf(lf[t] + m_old - m_new), expf(li[t] - m_new), expf(-m_new), 0.f);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) ms[0] = ms[n];
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *m_rec = ms[0];
+}
+
+// P lanes a column, R rows a lane: P * R >= d.  Rows beyond d are zeros and stay zeros.
+template <int R>
+__global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
+    const float* __restrict__ rows, int stride, int H, int d, int dv, int P,
+    const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ state,
+    long long rec, const float* __restrict__ gate, float* __restrict__ num, float q_scale) {
+    rv_pdl_launch_dependents();
+    const int h = blockIdx.y, r = blockIdx.z;
+    const int slot = state_slot[r];
+    const int a0 = q_start[r], a1 = q_start[r + 1];
+    rv_pdl_wait();
+    if (slot < 0 || a1 <= a0) return;
+    extern __shared__ __align__(16) float sm[];
+    const int DP = P * R;                        // padded rows
+    const int CPB = ML_THREADS / P;              // columns a block
+    float* qs = sm;                              // [ML_TC][DP]
+    float* ks = qs + ML_TC * DP;                 // [ML_TC][DP]
+    float* vs = ks + ML_TC * DP;                 // [ML_TC][CPB]
+    float* gs = vs + ML_TC * CPB;                // [ML_TC][2]
+    const int tid = threadIdx.x;
+    const int part = tid % P, cl = tid / P;
+    const int col = blockIdx.x * CPB + cl;       // dv: the column of n
+    const bool live = col <= dv;
+    const int r0 = part * R;
+    float S[R];
+    float* col_rec = state + (size_t)slot * rec + ((size_t)h * (dv + 1) + col) * d;
+#pragma unroll
+    for (int j = 0; j < R; ++j) S[j] = (live && r0 + j < d) ? col_rec[r0 + j] : 0.f;
+    const int q_off = h * d, k_off = H * d + h * d, v_off = 2 * H * d + h * dv;
+    const int W = dv + 1;
+    for (int c0 = a0; c0 < a1; c0 += ML_TC) {
+        const int n = min(ML_TC, a1 - c0);
+        __syncthreads();                         // the previous chunk has been used
+        for (int i = tid; i < n * DP; i += ML_THREADS) {
+            const int t = i / DP, x = i - t * DP;
+            const float* row = rows + (size_t)(c0 + t) * stride;
+            qs[i] = x < d ? row[q_off + x] * q_scale : 0.f;
+            ks[i] = x < d ? row[k_off + x] : 0.f;
+        }
+        for (int i = tid; i < n * CPB; i += ML_THREADS) {
+            const int t = i / CPB, c = blockIdx.x * CPB + (i - t * CPB);
+            vs[i] = c < dv ? rows[(size_t)(c0 + t) * stride + v_off + c] : 1.f;
+        }
+        for (int i = tid; i < n * 2; i += ML_THREADS) {
+            const int t = i >> 1;
+            gs[i] = gate[((size_t)(c0 + t) * H + h) * 4 + (i & 1)];
+        }
+        __syncthreads();
+        for (int t = 0; t < n; ++t) {
+            const float a = gs[2 * t], bv = gs[2 * t + 1] * vs[t * CPB + cl];
+            const float* kq = ks + t * DP + r0;
+            const float* qq = qs + t * DP + r0;
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < R; ++j) {
+                S[j] = fmaf(a, S[j], bv * kq[j]);
+                acc = fmaf(S[j], qq[j], acc);
+            }
+            for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (part == 0 && live) num[((size_t)(c0 + t) * H + h) * W + col] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int j = 0; j < R; ++j)
+            if (r0 + j < d) col_rec[r0 + j] = S[j];
+    }
+}
+
+template <typename T>
+__global__ void mlstm_finish_kernel(const float* __restrict__ num, const float* __restrict__ gate,
+                                    const float* __restrict__ rows, int stride, int g_off,
+                                    const float* __restrict__ norm_w, float eps,
+                                    const int* __restrict__ token_req,
+                                    const int* __restrict__ state_slot, T* __restrict__ out,
+                                    int n_tokens, int H, int dv) {
+    rv_pdl_launch_dependents();
+    const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= (long long)n_tokens * H) return;
+    const int t = (int)(warp / H), h = (int)(warp - (long long)t * H);
+    const bool pad = state_slot[token_req[t]] < 0;
+    rv_pdl_wait();
+    T* o = out + (size_t)t * H * dv + (size_t)h * dv;
+    if (pad) {
+        for (int c = lane; c < dv; c += 32) rv_store(o + c, 0.f);
+        return;
+    }
+    const float* nm = num + ((size_t)t * H + h) * (dv + 1);
+    const float den = fmaxf(fabsf(nm[dv]), gate[((size_t)t * H + h) * 4 + 2]) + 1e-6f;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) {
+        const float x = nm[c] / den;
+        ss += x * x;
+    }
+    ss = rv_warp_sum(ss);
+    const float rms = sqrtf(ss / (float)dv + eps);
+    const float* g = rows + (size_t)t * stride + g_off + h * dv;
+    const float* w = norm_w + h * dv;
+    for (int c = lane; c < dv; c += 32)
+        rv_store(o + c, nm[c] / den / rms * w[c] / (1.f + expf(-g[c])));
+}
+
+// Floats of one request's record.
+extern "C" long long rv_mlstm_record(int H, int d, int dv) {
+    return (long long)H * (dv + 1) * d + H;
+}
+
+// Floats of scratch for n tokens: gate [n, H, 4], then num [n, H, dv + 1].
+extern "C" long long rv_mlstm_scratch(int n_tokens, int H, int dv) {
+    return (long long)n_tokens * H * (4 + dv + 1);
+}
+
+static int ml_rows_per_lane(int d) { return d <= 64 ? 4 : d <= 256 ? 8 : 16; }
+
+extern "C" int rv_mlstm(const float* rows, int stride, const float* bi, const float* bf,
+                        const float* norm_w, float* state, const int* token_req, const int* q_start,
+                        const int* state_slot, float* scratch, void* out, int out_dtype,
+                        int n_tokens, int n_reqs, int H, int d, int dv, float cap, float eps,
+                        void* stream) {
+    if (n_tokens == 0 || n_reqs == 0) return 0;
+    if (n_tokens < 0 || n_reqs < 0 || H < 1 || d < 1 || dv < 1) RV_FAIL("mlstm: bad sizes");
+    if (d > 512) RV_FAIL("mlstm: key heads of %d exceed 512", d);
+    if (stride < 2 * H * d + 2 * H * dv + 2 * H) RV_FAIL("mlstm: rows are too short");
+    if (!(cap > 0.f)) RV_FAIL("mlstm: the gate cap must be positive");
+    if (n_reqs > 65535 || H > 65535) RV_FAIL("mlstm: too many requests or heads");
+    if ((uintptr_t)scratch & 15) RV_FAIL("mlstm: the scratch must be 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    const long long rec = rv_mlstm_record(H, d, dv);
+    const int i_off = 2 * H * d + H * dv, f_off = i_off + H, g_off = f_off + H;
+    float* gate = scratch;
+    float* num = scratch + (size_t)n_tokens * H * 4;
+    rv_launch(mlstm_gates_kernel, dim3(n_reqs, H), dim3(ML_THREADS), 0, s, rows, stride, i_off, f_off,
+              bi, bf, cap, q_start, state_slot, state, rec, H * (dv + 1) * d, gate, H);
+    RV_CHECK_LAUNCH("mlstm_gates");
+    const int R = ml_rows_per_lane(d);
+    int P = 1;
+    while (P * R < d) P <<= 1;
+    const int CPB = ML_THREADS / P;
+    const dim3 grid((dv + 1 + CPB - 1) / CPB, H, n_reqs);
+    const size_t smem = (size_t)(2 * ML_TC * P * R + ML_TC * CPB + 2 * ML_TC) * sizeof(float);
+    const float q_scale = 1.f / sqrtf((float)d);
+#define ML_SCAN(RR)                                                                               \
+    rv_launch(mlstm_scan_kernel<RR>, grid, dim3(ML_THREADS), smem, s, rows, stride, H, d, dv, P,  \
+              q_start, state_slot, state, rec, (const float*)gate, num, q_scale)
+    if (R == 4) ML_SCAN(4);
+    else if (R == 8) ML_SCAN(8);
+    else ML_SCAN(16);
+#undef ML_SCAN
+    RV_CHECK_LAUNCH("mlstm_scan");
+    const long long warps = (long long)n_tokens * H;
+    const long long blocks = (warps + 3) / 4;
+    if (blocks > 0x7fffffffLL) RV_FAIL("mlstm: too many tokens");
+    RV_DISPATCH_DTYPE(out_dtype, "mlstm",
+                      (rv_launch(mlstm_finish_kernel<T>, dim3((int)blocks), dim3(128), 0, s,
+                                 (const float*)num, (const float*)gate, rows, stride, g_off, norm_w,
+                                 eps, token_req, state_slot, (T*)out, n_tokens, H, dv)));
+    RV_CHECK_LAUNCH("mlstm_finish");
+    return 0;
+}

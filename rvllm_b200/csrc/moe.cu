@@ -10,13 +10,17 @@
 //                  weights = chosen s / (their sum + weight_eps).  One warp per token.
 //                  Options: score_mode 1 makes s the softmax of the logits over all experts
 //                  instead of their sigmoids; renorm 0 leaves the chosen s undivided; every
-//                  weight is multiplied by route_scale.
+//                  weight is multiplied by route_scale.  `choice_bias` float32 [E], if given,
+//                  is added to s wherever experts (and groups) are compared; the weights are
+//                  made from s without it.
 //   moe_route      the router's product (x [N, W] of any type, router float32 [E, W]) and the same
 //                  choice in one kernel.
 //   moe_gate_up    act[pair, f] = silu(<gate_e[f], x_t>) * <up_e[f], x_t> for pair = t * top + k,
 //                  e = ids[t, k]; gate_up is [E, 2F, W] with gate and up rows alternating
 //                  (row 2f: gate f, row 2f + 1: up f).  act_mode 1: with g = min(gate, limit) and
 //                  u = clamp(up, -limit, limit) the value is g * sigmoid(alpha g) * (u + 1).
+//                  act_mode 2: experts without a gate; the matrix is [E, F, W] and the value is
+//                  max(<up_e[f], x_t>, 0)^2.
 //   moe_down       out[t, w] = sum_k weights[t, k] * <down_e(k)[w], act[t * top + k]>, the sum in
 //                  the order of k; down is [E, W, F].  `addend` [N, W], if given, is where each sum
 //                  starts (the output of an expert that every token uses).
@@ -56,7 +60,9 @@ __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int
                                                 int keep, int group_top, float weight_eps,
                                                 int* __restrict__ ids, float* __restrict__ weights,
                                                 int lane, int score_mode = 0, int renorm = 1,
-                                                float route_scale = 1.f) {
+                                                float route_scale = 1.f,
+                                                const float* __restrict__ choice_bias = nullptr,
+                                                float* orig = nullptr) {
     if (score_mode == 1) {                           // softmax over all experts
         float m = -INFINITY;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, sc[e]);
@@ -71,6 +77,12 @@ __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int
         for (int e = lane; e < E; e += 32) sc[e] = sc[e] / tot;
     } else {
         for (int e = lane; e < E; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
+    }
+    if (choice_bias) {                               // compare s + bias, weigh with s
+        for (int e = lane; e < E; e += 32) {
+            orig[e] = sc[e];
+            sc[e] += choice_bias[e];
+        }
     }
     __syncwarp();
     if (groups > 1) {
@@ -122,7 +134,7 @@ __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int
             __syncwarp();
         }
         for (int e = lane; e < E; e += 32)
-            if (gs[e / size] != INFINITY) sc[e] = -1.f;          // below every sigmoid
+            if (gs[e / size] != INFINITY) sc[e] = -3.0e38f;      // below every score
         __syncwarp();
     }
     float sum = 0.f, mine = 0.f;
@@ -131,6 +143,7 @@ __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int
         float v;
         int i;
         moe_warp_argmax(sc, 0, E, lane, v, i);
+        if (choice_bias) v = orig[i];
         sum += v;
         if (lane == (k & 31) && k < 32) {
             mine = v;
@@ -141,7 +154,7 @@ __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int
             weights[k] = v;                          // divided below
         }
         __syncwarp();
-        if (lane == 0) sc[i] = -2.f;
+        if (lane == 0) sc[i] = -INFINITY;            // taken: below the experts left out
         __syncwarp();
     }
     const float inv = (renorm ? 1.f / (sum + weight_eps) : 1.f) * route_scale;
@@ -156,18 +169,19 @@ __device__ __forceinline__ void moe_select_warp(float* sc, float* gs, int E, int
 __global__ void moe_select_kernel(const float* __restrict__ logits, int n_tokens, int E, int top,
                                   int groups, int keep, int group_top, float weight_eps,
                                   int* __restrict__ ids, float* __restrict__ weights, int score_mode,
-                                  int renorm, float route_scale) {
+                                  int renorm, float route_scale,
+                                  const float* __restrict__ choice_bias) {
     rv_pdl_prologue();
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int t = blockIdx.x * (blockDim.x >> 5) + wib;
     if (t >= n_tokens) return;
-    float* sc = smem + (size_t)wib * (E + groups);       // [E] scores, then [groups]
+    float* sc = smem + (size_t)wib * (2 * E + groups);   // [E] scores, [groups], [E] unbiased scores
     for (int e = lane; e < E; e += 32) sc[e] = logits[(size_t)t * E + e];
     __syncwarp();
     moe_select_warp(sc, sc + E, E, top, groups, keep, group_top, weight_eps,
                     ids + (size_t)t * top, weights + (size_t)t * top, lane, score_mode, renorm,
-                    route_scale);
+                    route_scale, choice_bias, sc + E + groups);
 }
 
 // The router's product and the choice in one kernel: a block takes MOE_ROUTE_TOK tokens; each
@@ -194,13 +208,14 @@ template <typename T>
 __global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
     const T* __restrict__ x, const float* __restrict__ router, int n_tokens, int W, int E, int top,
     int groups, int keep, int group_top, float weight_eps, int* __restrict__ ids,
-    float* __restrict__ weights, int stage_rows, int score_mode, int renorm, float route_scale) {
+    float* __restrict__ weights, int stage_rows, int score_mode, int renorm, float route_scale,
+    const float* __restrict__ choice_bias) {
     rv_pdl_prologue();
-    extern __shared__ __align__(16) float smem[];        // [MOE_ROUTE_TOK][E + groups], then the rows
+    extern __shared__ __align__(16) float smem[];        // [MOE_ROUTE_TOK][2 E + groups], then the rows
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t0 = blockIdx.x * MOE_ROUTE_TOK;
     const int nt = min(MOE_ROUTE_TOK, n_tokens - t0);
-    const int stride = E + groups;
+    const int stride = 2 * E + groups;
     // eight values a lane and step (16-byte loads) when the width allows
     const bool vec = W % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)router & 15) == 0;
     // The block's rows go to shared memory first (one round trip for all of them), so that the
@@ -259,7 +274,7 @@ __global__ void __launch_bounds__(MOE_ROUTE_TOK * 32) moe_route_kernel(
         int* my_ids = ids + (size_t)(t0 + warp) * top;
         float* my_weights = weights + (size_t)(t0 + warp) * top;
         moe_select_warp(sc, sc + E, E, top, groups, keep, group_top, weight_eps, my_ids, my_weights,
-                        lane, score_mode, renorm, route_scale);
+                        lane, score_mode, renorm, route_scale, choice_bias, sc + E + groups);
     }
 }
 
@@ -279,8 +294,19 @@ __global__ void moe_gate_up_kernel(const T* __restrict__ x, const int* __restric
     __syncthreads();
     if (e < 0 || e >= E) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    const T* wg = gate_up + (size_t)e * 2 * F * W;
     const int f_end = min(F, (int)(blockIdx.y + 1) * MOE_ROWS);
+    if (act_mode == 2) {                               // no gate: [E, F, W], relu squared
+        const T* wu = gate_up + (size_t)e * F * W;
+        for (int f = blockIdx.y * MOE_ROWS + warp; f < f_end; f += nwarps) {
+            const T* u_row = wu + (size_t)f * W;
+            float u = 0.f;
+            for (int i = lane; i < W; i += 32) u += xs[i] * rv_load(u_row + i);
+            u = fmaxf(rv_warp_sum(u), 0.f);
+            if (lane == 0) rv_store(act + (size_t)pair * F + f, u * u);
+        }
+        return;
+    }
+    const T* wg = gate_up + (size_t)e * 2 * F * W;
     for (int f = blockIdx.y * MOE_ROWS + warp; f < f_end; f += nwarps) {
         const T* g_row = wg + (size_t)(2 * f) * W;
         const T* u_row = g_row + W;
@@ -336,7 +362,8 @@ __global__ void moe_down_kernel(const T* __restrict__ act, const int* __restrict
 
 extern "C" int rv_moe_select(const float* logits, int n_tokens, int E, int top, int groups,
                              int keep, int group_top, float weight_eps, int* ids, float* weights,
-                             int score_mode, int renorm, float route_scale, void* stream) {
+                             int score_mode, int renorm, float route_scale, const float* choice_bias,
+                             void* stream) {
     if (n_tokens == 0) return 0;
     if (n_tokens < 0 || E < 1 || top < 1 || top > E) RV_FAIL("moe_select: bad sizes");
     if (groups < 1 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < top)
@@ -345,11 +372,11 @@ extern "C" int rv_moe_select(const float* logits, int n_tokens, int E, int top, 
     if (group_top < 1 || group_top > MOE_MAX_GROUP_TOP)
         RV_FAIL("moe_select: a group's score sums 1 to %d scores", MOE_MAX_GROUP_TOP);
     const int wpb = 4;
-    const size_t smem = (size_t)wpb * (E + groups) * sizeof(float);
+    const size_t smem = (size_t)wpb * (2 * E + groups) * sizeof(float);
     if (smem > 48 * 1024) RV_FAIL("moe_select: too many experts");
     rv_launch(moe_select_kernel, dim3((n_tokens + wpb - 1) / wpb), dim3(wpb * 32), smem,
               (cudaStream_t)stream, logits, n_tokens, E, top, groups, keep, group_top, weight_eps,
-              ids, weights, score_mode, renorm, route_scale);
+              ids, weights, score_mode, renorm, route_scale, choice_bias);
     RV_CHECK_LAUNCH("moe_select");
     return 0;
 }
@@ -357,7 +384,7 @@ extern "C" int rv_moe_select(const float* logits, int n_tokens, int E, int top, 
 extern "C" int rv_moe_route(const void* x, int dtype, const float* router, int n_tokens, int W,
                             int E, int top, int groups, int keep, int group_top, float weight_eps,
                             int* ids, float* weights, int score_mode, int renorm, float route_scale,
-                            void* stream) {
+                            const float* choice_bias, void* stream) {
     if (n_tokens == 0) return 0;
     if (n_tokens < 0 || W < 1 || E < 1 || top < 1 || top > E) RV_FAIL("moe_route: bad sizes");
     if (groups < 1 || E % groups || keep < 1 || keep > groups || keep * (E / groups) < top)
@@ -365,7 +392,7 @@ extern "C" int rv_moe_route(const void* x, int dtype, const float* router, int n
                 keep, top);
     if (group_top < 1 || group_top > MOE_MAX_GROUP_TOP)
         RV_FAIL("moe_route: a group's score sums 1 to %d scores", MOE_MAX_GROUP_TOP);
-    size_t smem = (size_t)((MOE_ROUTE_TOK * (E + groups) + 3) & ~3) * sizeof(float);
+    size_t smem = (size_t)((MOE_ROUTE_TOK * (2 * E + groups) + 3) & ~3) * sizeof(float);
     if (smem > 40 * 1024) RV_FAIL("moe_route: too many experts");
     // the block's rows in shared memory when they fit beside the logits in 48 KB
     const size_t row_bytes = (size_t)MOE_ROUTE_TOK * W * (dtype == RV_DTYPE_BF16 ? 2 : 4);
@@ -376,7 +403,7 @@ extern "C" int rv_moe_route(const void* x, int dtype, const float* router, int n
                       (rv_launch(moe_route_kernel<T>, dim3(blocks), dim3(MOE_ROUTE_TOK * 32), smem,
                                  (cudaStream_t)stream, (const T*)x, router, n_tokens, W, E, top,
                                  groups, keep, group_top, weight_eps, ids, weights, stage_rows,
-                                 score_mode, renorm, route_scale)));
+                                 score_mode, renorm, route_scale, choice_bias)));
     RV_CHECK_LAUNCH("moe_route");
     return 0;
 }

@@ -138,14 +138,14 @@ __global__ void moe_combine_kernel(const bf16* __restrict__ ys, const int* __res
 // of K with one tile, 48 KB for two), each with an accumulator of its own in TMEM.
 // ACT: 0 = the sums as they are; 1 = silu(gate) * up; 2 = the clamped form
 //   g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(alpha g) * (u + 1)
-// of pairs of neighbouring rows of W.
+// of pairs of neighbouring rows of W; 3 = max(sum, 0)^2 of every row (experts without a gate).
 template <int ACT>
 __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     bf16* __restrict__ out, int* __restrict__ status, const int* __restrict__ tile_expert,
     const int* __restrict__ tile_row0, const int* __restrict__ n_tiles, int n_out, int kblocks,
     int TN, int stages, int MT, float limit, float alpha) {
-    constexpr bool SWIGLU = ACT != 0;
+    constexpr bool SWIGLU = ACT == 1 || ACT == 2;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int w_half = MG_BM * MG_BK * 2;                     // one tile of 128 rows of W
@@ -290,9 +290,14 @@ __global__ void __launch_bounds__(128, 2) moe_grouped_kernel(
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    stage_out[(c + j) * SW + n_local] =
-                        __float2bfloat16_rn(good ? __uint_as_float(r[j]) : 0.f);
+                for (int j = 0; j < 16; ++j) {
+                    float v = good ? __uint_as_float(r[j]) : 0.f;
+                    if (ACT == 3) {
+                        v = fmaxf(v, 0.f);
+                        v *= v;
+                    }
+                    stage_out[(c + j) * SW + n_local] = __float2bfloat16_rn(v);
+                }
             }
         }
         __syncthreads();
@@ -326,6 +331,9 @@ extern "C" int rv_moe_grouped_init() {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(moe_grouped_kernel<2>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_MAX);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(moe_grouped_kernel<3>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, MG_SMEM_MAX);
     if (e != cudaSuccess) RV_FAIL("moe_grouped: %s", cudaGetErrorString(e));
     if (!encode_fn()) RV_FAIL("moe_grouped: cuTensorMapEncodeTiled is not available in this driver");
     return 0;
@@ -351,7 +359,10 @@ static int grouped_product(const void* xs, const void* w, void* out, int* status
     if (stages < 2) stages = 2;
     const size_t smem = (size_t)stages * per_stage + 1024;
     dim3 grid((n_out + MT * MG_BM - 1) / (MT * MG_BM), max_tiles);
-    if (act == 2)
+    if (act == 3)
+        rv_launch(moe_grouped_kernel<3>, grid, dim3(128), smem, stream, map_w, map_x, (bf16*)out,
+                  status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages, MT, limit, alpha);
+    else if (act == 2)
         rv_launch(moe_grouped_kernel<2>, grid, dim3(128), smem, stream, map_w, map_x, (bf16*)out,
                   status, tile_expert, tile_row0, n_tiles, n_out, kblocks, TN, stages, MT, limit, alpha);
     else if (act == 1)
@@ -373,6 +384,8 @@ extern "C" long long rv_moe_grouped_scratch_bytes(int n_tokens, int top, int E, 
 }
 
 // x [n_tokens, W] bf16; gate_up [E, 2F, W] with gate and up rows alternating; down [E, W, F].
+// act_mode 2: experts without a gate, `gate_up` is the up matrices [E, F, W] and the activation
+// the square of relu.
 extern "C" int rv_moe_experts_grouped(const void* x, const int* ids, const float* weights,
                                       const void* gate_up, const void* down, void* out,
                                       void* scratch, long long scratch_bytes, int* status,
@@ -383,7 +396,7 @@ extern "C" int rv_moe_experts_grouped(const void* x, const int* ids, const float
     if (n_tokens < 0 || top < 1 || E < 1 || W < 8 || F < 8 || W % 8 || F % 8)
         RV_FAIL("moe_experts_grouped: widths must be multiples of 8");
     if (TN != 16 && TN != 32 && TN != 64 && TN != 128) RV_FAIL("moe_experts_grouped: bad token tile");
-    if (act_mode != 0 && act_mode != 1) RV_FAIL("moe_experts_grouped: unknown activation %d", act_mode);
+    if (act_mode < 0 || act_mode > 2) RV_FAIL("moe_experts_grouped: unknown activation %d", act_mode);
     if ((uintptr_t)addend & 15) RV_FAIL("moe_experts_grouped: the added rows must be 16-byte aligned");
     if ((size_t)3 * E * sizeof(int) > 48 * 1024) RV_FAIL("moe_experts_grouped: too many experts");
     const long long pairs = (long long)n_tokens * top;
@@ -411,8 +424,9 @@ extern "C" int rv_moe_experts_grouped(const void* x, const int* ids, const float
     rv_launch(moe_gather_kernel, dim3((unsigned)((rows + 7) / 8)), dim3(256), 0, s, (const bf16*)x,
               (const int*)sorted_token, xs, (int)rows, W);
     RV_CHECK_LAUNCH("moe_gather");
-    if (grouped_product(xs, gate_up, act, status, tile_expert, tile_row0, n_tiles, rows, E, 2 * F, W,
-                        TN, max_tiles, act_mode == 1 ? 2 : 1, limit, alpha, s))
+    if (grouped_product(xs, gate_up, act, status, tile_expert, tile_row0, n_tiles, rows, E,
+                        act_mode == 2 ? F : 2 * F, W, TN, max_tiles,
+                        act_mode == 2 ? 3 : act_mode == 1 ? 2 : 1, limit, alpha, s))
         return 1;
     if (grouped_product(act, down, ys, status, tile_expert, tile_row0, n_tiles, rows, E, W, F, TN,
                         max_tiles, 0, 0.f, 0.f, s))

@@ -51,6 +51,7 @@ class CudaOps:
         self.lib.rv_paged_attention_decode_scratch_bytes.restype = c_longlong
         self.lib.rv_gemm_tiled_bytes.restype = c_longlong
         self.lib.rv_gated_delta_scratch.restype = c_longlong
+        self.lib.rv_mlstm_scratch.restype = c_longlong
         self.lib.rv_paged_attention_mixed_scratch_bytes.restype = c_longlong
         self._scratch = {}
         self._retired = []
@@ -138,8 +139,10 @@ class CudaOps:
 
     # ---- residual add + RMSNorm ------------------------------------------------------
 
-    def add_rmsnorm(self, resid, delta, weight, eps, out, rows=None):
-        """`resid` None: the rows of `delta` alone are normalised (no stream involved)."""
+    def add_rmsnorm(self, resid, delta, weight, eps, out, rows=None, delta_scale=None, add=None):
+        """`resid` None: the rows of `delta` alone are normalised (no stream involved).
+        `delta_scale` float32 [hidden]: the pending rows are multiplied by it, channel by channel,
+        before they are added; `add` float32 [hidden]: one vector added to every row."""
         if resid is not None:
             self._need(resid, "residual stream", torch.float32)
         elif delta is None or rows is not None:
@@ -155,10 +158,17 @@ class CudaOps:
         n, hidden = out.shape
         if (resid if resid is not None else delta).shape[1] != hidden or weight.shape[0] != hidden:
             raise KernelError("add_rmsnorm: widths disagree")
-        self._check(self.lib.rv_add_rmsnorm(
+        for vec, what in ((delta_scale, "scale of the pending rows"), (add, "added vector")):
+            if vec is not None:
+                self._need(vec, what, torch.float32)
+                if vec.shape != (hidden,):
+                    raise KernelError(f"add_rmsnorm: the {what} has another width")
+        if delta_scale is not None and delta is None:
+            raise KernelError("add_rmsnorm: a scale without pending rows")
+        self._check(self.lib.rv_add_rmsnorm_ex(
             _ptr(resid), _ptr(delta), _code(delta.dtype) if delta is not None else _F32,
             _ptr(weight), _ptr(out), _code(out.dtype), _ptr(rows), c_int(n), c_int(hidden),
-            c_float(eps), self._stream()), "add_rmsnorm")
+            c_float(eps), _ptr(delta_scale), _ptr(add), self._stream()), "add_rmsnorm")
 
     # ---- matrix product (library) -------------------------------------------------------
 
@@ -938,13 +948,21 @@ class CudaOps:
     # ---- mixture of experts ---------------------------------------------------------------
 
     SCORE_MODES = {"sigmoid": 0, "softmax": 1}
-    EXPERT_ACTIVATIONS = {"swiglu": 0, "glu_clamp": 1}
+    EXPERT_ACTIVATIONS = {"swiglu": 0, "glu_clamp": 1, "relu2": 2}
+
+    def _choice_bias(self, choice_bias, experts):
+        if choice_bias is not None:
+            self._need(choice_bias, "choice bias", torch.float32)
+            if choice_bias.shape != (experts,):
+                raise KernelError("the choice bias has one number per expert")
+        return _ptr(choice_bias)
 
     def moe_select(self, logits, groups, keep, group_top, weight_eps, ids, weights,
-                   score="sigmoid", renormalize=True, route_scale=1.0):
+                   score="sigmoid", renormalize=True, route_scale=1.0, choice_bias=None):
         """`score`: how logits become scores ("sigmoid", or "softmax" over all experts);
         `renormalize` false: the chosen scores are not divided by their sum; every weight is
-        multiplied by `route_scale`."""
+        multiplied by `route_scale`; `choice_bias` float32 [experts] is added to the scores
+        where experts are compared, not where they are weighed."""
         self._need(logits, "router logits", torch.float32)
         self._need(ids, "expert ids", torch.int32)
         self._need(weights, "expert weights", torch.float32)
@@ -953,10 +971,10 @@ class CudaOps:
             _ptr(logits), c_int(n), c_int(experts), c_int(ids.shape[1]), c_int(groups),
             c_int(keep), c_int(group_top), c_float(weight_eps), _ptr(ids), _ptr(weights),
             c_int(self.SCORE_MODES[score]), c_int(1 if renormalize else 0), c_float(route_scale),
-            self._stream()), "moe_select")
+            self._choice_bias(choice_bias, experts), self._stream()), "moe_select")
 
     def moe_route(self, x, router, groups, keep, group_top, weight_eps, ids, weights,
-                  score="sigmoid", renormalize=True, route_scale=1.0):
+                  score="sigmoid", renormalize=True, route_scale=1.0, choice_bias=None):
         """The router's product (float32 `router` [experts, width], float32 sums) and the
         choice of `moe_select`, in one kernel."""
         self._need(x, "feed-forward input")
@@ -970,14 +988,17 @@ class CudaOps:
             _ptr(x), _code(x.dtype), _ptr(router), c_int(x.shape[0]), c_int(width), c_int(experts),
             c_int(ids.shape[1]), c_int(groups), c_int(keep), c_int(group_top), c_float(weight_eps),
             _ptr(ids), _ptr(weights), c_int(self.SCORE_MODES[score]),
-            c_int(1 if renormalize else 0), c_float(route_scale), self._stream()), "moe_route")
+            c_int(1 if renormalize else 0), c_float(route_scale),
+            self._choice_bias(choice_bias, experts), self._stream()), "moe_route")
 
     def moe_experts(self, x, ids, weights, gate_up, down, out, activation="swiglu", limit=0.0,
                     alpha=1.0, addend=None):
         """out[t] = sum_k weights[t, k] * down[e](act(gate[e] x_t, up[e] x_t)), e = ids[t, k];
         gate_up [E, 2F, W] (gate and up rows alternating), down [E, W, F].  `activation`
         "swiglu": silu(gate) * up; "glu_clamp": g = min(gate, limit), u = clamp(up, -limit,
-        limit), g * sigmoid(alpha g) * (u + 1).  `addend` [N, W]: rows each sum starts from."""
+        limit), g * sigmoid(alpha g) * (u + 1); "relu2": experts without a gate, `gate_up` is
+        the up matrices [E, F, W] and the activation max(., 0)^2.  `addend` [N, W]: rows each sum
+        starts from."""
         act_mode = self.EXPERT_ACTIVATIONS[activation]
         if addend is not None:
             self._need(addend, "rows added to the experts' output", x.dtype)
@@ -989,7 +1010,8 @@ class CudaOps:
         self._need(out, "feed-forward output", x.dtype)
         n, top = ids.shape
         experts, width, ffn = down.shape
-        if gate_up.shape != (experts, 2 * ffn, width) or x.shape[1] != width:
+        first_rows = ffn if activation == "relu2" else 2 * ffn
+        if gate_up.shape != (experts, first_rows, width) or x.shape[1] != width:
             raise KernelError("moe_experts: shapes disagree")
         grouped = (x.dtype == torch.bfloat16 and width % 8 == 0 and ffn % 8 == 0
                    and self.moe_mode != "simple"
@@ -1125,6 +1147,103 @@ class CudaOps:
         self._check(self.lib.rv_glu_clamp(_ptr(gate_up), _ptr(bias), _ptr(out), _code(out.dtype),
                                           c_int(n), c_int(f), c_float(limit), c_float(alpha),
                                           self._stream()), "glu_clamp")
+
+    # ---- relu squared; a sum of two mixers -------------------------------------------------
+
+    def relu2(self, z, out):
+        self._need(z, "activation input")
+        self._need(out, "activation output", z.dtype)
+        if z.shape != out.shape:
+            raise KernelError("relu2: shapes disagree")
+        self._check(self.lib.rv_relu2(_ptr(z), _ptr(out), _code(z.dtype), c_int(z.shape[0]),
+                                      c_int(z.shape[1]), self._stream()), "relu2")
+
+    def weighted_sum(self, a, sa, b, sb, out):
+        """out = sa * a + sb * b, float32 arithmetic."""
+        self._need(a, "first summand")
+        self._need(b, "second summand", a.dtype)
+        self._need(out, "sum", a.dtype)
+        if a.shape != b.shape or a.shape != out.shape:
+            raise KernelError("weighted_sum: shapes disagree")
+        self._check(self.lib.rv_weighted_sum(_ptr(a), c_float(sa), _ptr(b), c_float(sb), _ptr(out),
+                                             _code(a.dtype), c_longlong(a.numel()), self._stream()),
+                    "weighted_sum")
+
+    # ---- latent rows with a query latent and a turned key part ------------------------------
+
+    def latent_prepare(self, rows, q_off, q_rank, q_weight, cq, kv_off, rank, rot, kv_weight, eps,
+                       freq, positions, slot_mapping, cache):
+        """Columns [q_off, +q_rank) of `rows` RMS-normed into `cq` (q_rank 0: none); columns
+        [kv_off, +rank) RMS-normed and the `rot` columns after them turned by the position, both
+        into the token's page slot [rank + rot]."""
+        self._need(rows, "latent rows")
+        self._need(kv_weight, "latent norm weight", torch.float32)
+        self._need(cache, "latent pages", rows.dtype)
+        if kv_weight.shape[0] != rank or cache.shape[-1] * cache.shape[-2] != rank + rot:
+            raise KernelError("latent_prepare: the rank and the pages disagree")
+        if q_rank:
+            self._need(q_weight, "query latent norm weight", torch.float32)
+            self._need(cq, "query latent rows", rows.dtype)
+            if q_weight.shape[0] != q_rank or cq.shape != (rows.shape[0], q_rank):
+                raise KernelError("latent_prepare: the query latent has another size")
+        if rot:
+            self._need(freq, "rotation frequencies", torch.float32)
+            if freq.shape[0] != rot // 2:
+                raise KernelError("latent_prepare: one frequency per turning pair")
+        self._check(self.lib.rv_latent_prepare(
+            _ptr(rows), _code(rows.dtype), c_int(rows.shape[1]), c_int(rows.shape[0]), c_int(q_off),
+            c_int(q_rank), _ptr(q_weight), _ptr(cq), c_int(kv_off), c_int(rank), c_int(rot),
+            _ptr(kv_weight), c_float(eps), _ptr(freq), _ptr(positions), _ptr(slot_mapping),
+            _ptr(cache), self._stream()), "latent_prepare")
+
+    def rope_heads(self, x, heads, size, off, rot, freq, positions):
+        """In every head of x [N, heads * size] the `rot` values from `off` on turn by the
+        token's position (dimension i with i + rot/2, angle position * freq[i])."""
+        if not rot:
+            return
+        self._need(x, "rows to turn")
+        self._need(freq, "rotation frequencies", torch.float32)
+        if freq.shape[0] != rot // 2 or x.shape[1] < heads * size:
+            raise KernelError("rope_heads: sizes disagree")
+        self._check(self.lib.rv_rope_heads(
+            _ptr(x), _code(x.dtype), c_int(x.shape[1]), c_int(x.shape[0]), c_int(heads), c_int(size),
+            c_int(off), c_int(rot), _ptr(freq), _ptr(positions), self._stream()), "rope_heads")
+
+    def head_gate(self, x, heads, size, rows, gate_off):
+        """x[n, h, :] <- x[n, h, :] * sigmoid(rows[n, gate_off + h])."""
+        self._need(x, "heads to gate")
+        self._need(rows, "rows with the gates", x.dtype)
+        if x.shape[1] != heads * size:
+            raise KernelError("head_gate: sizes disagree")
+        self._check(self.lib.rv_head_gate(
+            _ptr(x), _code(x.dtype), c_int(x.shape[0]), c_int(heads), c_int(size), _ptr(rows),
+            c_int(rows.shape[1]), c_int(gate_off), self._stream()), "head_gate")
+
+    # ---- matrix memory with exponential gates ------------------------------------------------
+
+    def mlstm_record(self, heads, dim, vdim) -> int:
+        """Floats of one request's record: per head vdim + 1 columns of dim rows, then the maxima."""
+        return heads * (vdim + 1) * dim + heads
+
+    def mlstm(self, rows, in_bias, forget_bias, norm_w, state, ctx, out, heads, dim, vdim, cap, eps):
+        """The matrix memory over the step's tokens; see csrc/mlstm.cu for the layout of `rows`
+        (q | k | v | i | f | g, float32) and of the record."""
+        for t, what in ((rows, "projection rows"), (in_bias, "input gate bias"),
+                        (forget_bias, "forget gate bias"), (norm_w, "output norm weight"),
+                        (state, "state records")):
+            self._need(t, what, torch.float32)
+        self._need(out, "mixer output")
+        if state.shape[1] != self.mlstm_record(heads, dim, vdim) or out.shape[1] != heads * vdim:
+            raise KernelError("mlstm: the record or the output has another size")
+        n = rows.shape[0]
+        need = self.lib.rv_mlstm_scratch(c_int(n), c_int(heads), c_int(vdim))
+        scratch = torch.empty((need,), dtype=torch.float32, device=rows.device)
+        self._check(self.lib.rv_mlstm(
+            _ptr(rows), c_int(rows.shape[1]), _ptr(in_bias), _ptr(forget_bias), _ptr(norm_w),
+            _ptr(state), _ptr(ctx.token_req), _ptr(ctx.q_start), _ptr(ctx.state_slot),
+            _ptr(scratch), _ptr(out), _code(out.dtype), c_int(n), c_int(ctx.n_reqs), c_int(heads),
+            c_int(dim), c_int(vdim), c_float(cap), c_float(eps), self._stream()), "mlstm")
+        self.launches += 2
 
     def softcap(self, logits, cap):
         self._need(logits, "logits", torch.float32)

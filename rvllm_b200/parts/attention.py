@@ -24,7 +24,9 @@ softmax's denominator holds one more term exp(sink) without a key or a value, a 
 head, no weight).  A query temperature (`q_temp` = (coef, every)): the query at position p is
 multiplied by 1 + coef ln(floor((p + 1) / every) + 1), so scores grow slowly with the length
 of the context.  With the unit norm, the temperature or a value size of its own, norm,
-temperature and the cache write are `ops.qk_unit_write` after the one q|k|v product.
+temperature and the cache write are `ops.qk_unit_write` after the one q|k|v product.  A gate
+per head (`head_gate`): head j's result is multiplied by sigmoid(W_g x)_j before the output
+product; W_g's rows ride at the end of the q|k|v product and `ops.head_gate` applies them.
 
 A third form (`_prepared`), chosen by any of: biases on the q, k and v projections (`bias`); a
 norm over the whole query projection and one over the whole key projection, before the split
@@ -51,6 +53,7 @@ class Attention(Mixer):
         n = spec.names
         return {k: n.get(k, k + ".weight") for k in
                 ("q_proj", "k_proj", "v_proj", "out_proj", "q_norm", "k_norm", "sink")} | \
+            {"head_gate": n.get("head_gate", "g")} | \
             {k: n.get(k, d) for k, d in (("q_bias", "q_proj.bias"), ("k_bias", "k_proj.bias"),
                                          ("v_bias", "v_proj.bias"), ("vmix", "vmix"))}
 
@@ -81,6 +84,11 @@ class Attention(Mixer):
             p[n["vmix"]] = ParamDecl((), "normal", mean=0.5, std=0.2)
         if spec.sinks:
             p[n["sink"]] = ParamDecl((spec.num_heads,), "normal", mean=0.0, std=1.0)
+        if spec.head_gate:
+            if Attention._prepared(spec):
+                raise ValueError("attention: a gate per head goes with no bias, whole-projection "
+                                 "norm, pairwise rotation or value mixing")
+            p[n["head_gate"]] = ParamDecl((spec.num_heads, spec.hidden), "linear")
         return p
 
     @staticmethod
@@ -97,7 +105,8 @@ class Attention(Mixer):
     def _plain(spec) -> bool:
         """Whether the layer is the plain form that the fused q|k|v kernel serves."""
         return (not spec.v_head_dim or spec.v_head_dim == spec.head_dim) and \
-            spec.q_temp is None and (spec.qk_norm is None or spec.qk_norm.kind != "rms_unit")
+            spec.q_temp is None and (spec.qk_norm is None or spec.qk_norm.kind != "rms_unit") \
+            and not spec.head_gate
 
     @staticmethod
     def cache_need(spec: AttentionSpec):
@@ -122,12 +131,15 @@ class Attention(Mixer):
         n = self._names(spec)
         q = tensors[n["q_proj"]]
         self.has_kv = n["k_proj"] in tensors
+        gate = [tensors[n["head_gate"]].to(q.dtype)] if spec.head_gate else []
         if self.has_kv:
             self.w_qkv = torch.cat([q, tensors[n["k_proj"]].to(q.dtype),
-                                    tensors[n["v_proj"]].to(q.dtype)], dim=0).contiguous()
+                                    tensors[n["v_proj"]].to(q.dtype)] + gate, dim=0).contiguous()
         else:
-            self.w_qkv = q.contiguous()
-        self.w_q = self.w_qkv[:spec.num_heads * spec.head_dim]
+            self.w_qkv = torch.cat([q] + gate, dim=0).contiguous()
+        # a call that reads another call's pages multiplies q (and the gate) only
+        self.w_q = self.w_qkv[:spec.num_heads * spec.head_dim] if not gate else \
+            torch.cat([q] + gate, dim=0).contiguous()
         self.w_out = tensors[n["out_proj"]].contiguous()
         self.q_norm = self.k_norm = None
         self.v_dim = spec.v_head_dim or spec.head_dim
@@ -194,6 +206,9 @@ class Attention(Mixer):
         self.ops.paged_attention(rows, s.num_heads, s.num_kv_heads, s.head_dim,
                                  cache.k, cache.v, ctx, group, self.scale, s.window, out,
                                  sinks=self.sinks, v_head_dim=self.v_dim)
+        if s.head_gate:
+            self.ops.head_gate(out, s.num_heads, self.v_dim, rows,
+                               rows.shape[1] - s.num_heads)
         return self.ops.linear(out, self.w_out, out_dtype=self.dtype)
 
 

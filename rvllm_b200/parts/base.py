@@ -50,6 +50,13 @@ class PagedNeed:
 
 
 @dataclass(frozen=True)
+class SeveralNeeds:
+    """What a mixer made of several mixers has to remember: one need (or None) per branch, in
+    the branches' order.  The call's cache view then has `parts`, one view (or None) each."""
+    parts: Tuple[object, ...]
+
+
+@dataclass(frozen=True)
 class StateNeed:
     """A float32 record of this shape per live request.  The cache manager hands a request
     its slot with the record cleared to zero, so the state before position 0 is zero
@@ -174,6 +181,10 @@ class Stream:
     pending_norm: Optional[object] = None   # a Norm `pending` has to pass through first
     pending_hyper: Optional[tuple] = None   # (mix [S, S], out [S]): how `pending` enters the
                                             # streams of a block with hyper-connections
+    pending_scale: Optional[object] = None  # float32 [hidden]: `pending` is multiplied by it,
+                                            # channel by channel, as it is added
+    pending_add: Optional[object] = None    # float32 [hidden]: one vector that every row of the
+                                            # stream still has to receive
 
 
 _MIXERS: Dict[str, type] = {}

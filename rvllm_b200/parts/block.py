@@ -6,12 +6,17 @@ mixer's and the feed-forward's output before each addition (src/model.rs:571, 58
 LFM2 uses neither).  The residual stream is float32; each sub-layer's output stays pending and is
 added by the next norm's kernel, together with the norm it still has to pass through when
 the block has one after the sub-layer.  A block without a feed-forward is its first half.
+A block may scale each sub-layer's output channel by channel before the addition (a learned
+vector per sub-layer and one factor for the whole model); the scale travels with the pending
+rows and is applied by the same kernel.
 """
 from __future__ import annotations
 
 from .base import (Arrangement, Stream, feed_forward_class, mixer_class, norm_class,
                    register_arrangement)
-from .spec import BlockSpec
+import torch
+
+from .spec import BlockSpec, ParamDecl
 
 
 def _sub(tensors, prefix):
@@ -38,6 +43,17 @@ def norm_params(norm, name):
 def build_norm(norm, name, tensors, ops, dtype):
     names = norm_tensor_names(norm, name)
     return norm_class(norm.kind)(norm, {k: tensors[n] for k, n in names.items()}, ops, dtype)
+
+
+def stream_options(stream: Stream) -> dict:
+    """What a norm's `add_norm` has to be told beyond the pending rows: their scale and a vector
+    still to be added.  Only norms that take these options are ever given them."""
+    options = {}
+    if stream.pending_scale is not None and stream.pending is not None:
+        options["delta_scale"] = stream.pending_scale
+    if stream.pending_add is not None:
+        options["add"] = stream.pending_add
+    return options
 
 
 class PreNormBlock(Arrangement):
@@ -74,6 +90,10 @@ class PreNormBlock(Arrangement):
                 out[spec.ffn_prefix + k] = d
         for norm, name in spec.norms.values():
             out.update(norm_params(norm, name))
+        for place, name in spec.layer_scale.items():
+            if place not in ("mixer", "ffn") or (place == "ffn" and spec.feed_forward is None):
+                raise ValueError(f"a pre_norm block has no sub-layer {place!r} to scale")
+            out[name] = ParamDecl((spec.mixer.hidden,), "norm")
         return out
 
     def __init__(self, spec: BlockSpec, tensors, ops, dtype):
@@ -94,15 +114,30 @@ class PreNormBlock(Arrangement):
         self.mixer_norm, self.ffn_norm = build("mixer"), build("ffn")
         self.post_mixer, self.post_ffn = build("post_mixer"), build("post_ffn")
 
+        def scale(place):
+            """float32 [hidden]: residual_scale times the sub-layer's learned scale, or None."""
+            name = spec.layer_scale.get(place)
+            if name is None and spec.residual_scale == 1.0:
+                return None
+            if name is None:
+                some = next(iter(tensors.values()))
+                return torch.full((spec.mixer.hidden,), float(spec.residual_scale),
+                                  dtype=torch.float32, device=some.device)
+            return (tensors[name].to(torch.float32) * float(spec.residual_scale)).contiguous()
+
+        self.mixer_scale, self.ffn_scale = scale("mixer"), scale("ffn")
+
     def forward(self, stream: Stream, ctx, cache) -> Stream:
         normed = self.mixer_norm.add_norm(stream.resid, stream.pending, ctx,
-                                          delta_norm=stream.pending_norm)
+                                          delta_norm=stream.pending_norm, **stream_options(stream))
         mixed = self.mixer.forward(normed, ctx, cache)
         if self.feed_forward is None:
-            return Stream(stream.resid, mixed, self.post_mixer)
-        normed2 = self.ffn_norm.add_norm(stream.resid, mixed, ctx, delta_norm=self.post_mixer)
+            return Stream(stream.resid, mixed, self.post_mixer, pending_scale=self.mixer_scale)
+        options = {} if self.mixer_scale is None else {"delta_scale": self.mixer_scale}
+        normed2 = self.ffn_norm.add_norm(stream.resid, mixed, ctx, delta_norm=self.post_mixer,
+                                         **options)
         out = self.feed_forward.forward(normed2, ctx)
-        return Stream(stream.resid, out, self.post_ffn)
+        return Stream(stream.resid, out, self.post_ffn, pending_scale=self.ffn_scale)
 
 
 register_arrangement("pre_norm", PreNormBlock)

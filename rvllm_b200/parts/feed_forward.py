@@ -50,8 +50,9 @@ class Dense(FeedForward):
         z > 0:   softplus(p) z^2 + z/2
         z <= 0:  (1/2 + softplus(q)) (e^z - 1 - z) + z/2
     so the slope at 0 is 1/2 from both sides.
+    "relu2": max(z, 0)^2, nothing learned.
     """
-    ACTIVATIONS = {"xielu": 2}          # name -> how many learned numbers it has
+    ACTIVATIONS = {"xielu": 2, "relu2": 0}      # name -> how many learned numbers it has
 
     @staticmethod
     def params(spec: DenseSpec):
@@ -73,12 +74,16 @@ class Dense(FeedForward):
         n = spec.names
         self.up = tensors[n.get("up", "up.weight")].contiguous()
         self.down = tensors[n.get("down", "down.weight")].contiguous()
-        self.act = tensors[n.get("act", "act")].to(torch.float32).contiguous()
+        self.act = tensors[n.get("act", "act")].to(torch.float32).contiguous() \
+            if self.ACTIVATIONS[spec.activation] else None
 
     def forward(self, normed, ctx):
         z = self.ops.linear(normed, self.up, out_dtype=self.dtype)
         act = self.ops.new_rows(normed.shape[0], self.spec.ffn_dim, self.dtype, normed.device)
-        self.ops.xielu(z, self.act, act)
+        if self.spec.activation == "relu2":
+            self.ops.relu2(z, act)
+        else:
+            self.ops.xielu(z, self.act, act)
         return self.ops.linear(act, self.down, out_dtype=self.dtype)
 
 
@@ -153,15 +158,18 @@ class MoE(FeedForward):
     Options of the spec: scores that are the softmax of the router logits over all experts;
     chosen scores that are not divided by their sum; a factor on every weight; experts of the
     clamped form (`GluClamp`); a shared feed-forward that every token passes, whose output is
-    where the experts' weighted sum starts.
+    where the experts' weighted sum starts; experts without a gate, down_e(max(up_e x, 0)^2)
+    (`activation` "relu2": no "gate" tensors, the stack is [experts, ffn, hidden]); a learned
+    number per expert that is added to the scores where experts are compared and nowhere else
+    (`choice_bias`, tensor "correction").
     """
     SCORES = ("sigmoid", "softmax")
-    ACTIVATIONS = ("swiglu", "glu_clamp")
+    ACTIVATIONS = ("swiglu", "glu_clamp", "relu2")
 
     @staticmethod
     def _names(spec):
         n = spec.names
-        out = {"router": n.get("router", "router")}
+        out = {"router": n.get("router", "router"), "correction": n.get("correction", "correction")}
         for e in range(spec.experts):
             for k in ("gate", "up", "down"):
                 out[(e, k)] = n.get("expert", "e{e}.{k}").format(e=e, k=k)
@@ -189,8 +197,11 @@ class MoE(FeedForward):
         n = MoE._names(spec)
         p = {n["router"]: ParamDecl((spec.experts, spec.hidden), "normal", mean=0.0,
                                     std=spec.hidden ** -0.5)}
+        if spec.choice_bias:
+            p[n["correction"]] = ParamDecl((spec.experts,), "normal", mean=0.0, std=0.1)
         for e in range(spec.experts):
-            p[n[(e, "gate")]] = ParamDecl((spec.ffn_dim, spec.hidden), "linear")
+            if spec.activation != "relu2":
+                p[n[(e, "gate")]] = ParamDecl((spec.ffn_dim, spec.hidden), "linear")
             p[n[(e, "up")]] = ParamDecl((spec.ffn_dim, spec.hidden), "linear")
             p[n[(e, "down")]] = ParamDecl((spec.hidden, spec.ffn_dim), "linear")
         if spec.shared is not None:
@@ -207,12 +218,18 @@ class MoE(FeedForward):
         self.dtype = dtype
         n = self._names(spec)
         self.router = tensors[n["router"]].to(torch.float32).contiguous()
-        first = tensors[n[(0, "gate")]]
-        self.gate_up = torch.stack([
-            torch.stack([tensors[n[(e, "gate")]].to(first.dtype),
-                         tensors[n[(e, "up")]].to(first.dtype)], dim=1).reshape(
-                             2 * spec.ffn_dim, spec.hidden)
-            for e in range(spec.experts)]).contiguous()          # [E, 2F, W]: gate f, up f, ...
+        self.choice_bias = tensors[n["correction"]].to(torch.float32).contiguous() \
+            if spec.choice_bias else None
+        first = tensors[n[(0, "up")]]
+        if spec.activation == "relu2":
+            self.gate_up = torch.stack([tensors[n[(e, "up")]].to(first.dtype)
+                                        for e in range(spec.experts)]).contiguous()   # [E, F, W]
+        else:
+            self.gate_up = torch.stack([
+                torch.stack([tensors[n[(e, "gate")]].to(first.dtype),
+                             tensors[n[(e, "up")]].to(first.dtype)], dim=1).reshape(
+                                 2 * spec.ffn_dim, spec.hidden)
+                for e in range(spec.experts)]).contiguous()      # [E, 2F, W]: gate f, up f, ...
         self.down = torch.stack([tensors[n[(e, "down")]].to(first.dtype)
                                  for e in range(spec.experts)]).contiguous()   # [E, W, F]
         self.shared = None
@@ -230,6 +247,8 @@ class MoE(FeedForward):
         extra = {}
         if s.score != "sigmoid" or not s.renormalize or s.route_scale != 1.0:
             extra = dict(score=s.score, renormalize=s.renormalize, route_scale=s.route_scale)
+        if self.choice_bias is not None:
+            extra["choice_bias"] = self.choice_bias
         self.ops.moe_route(normed, self.router, s.groups, s.keep, s.group_top, s.weight_eps,
                            ids, weights, **extra)
         out = self.ops.new_rows(n, s.hidden, self.dtype, normed.device)

@@ -14,8 +14,8 @@ import torch
 import dataclasses
 
 from .base import PagedNeed, Stream, arrangement_class, mixer_class, norm_class
-from .block import build_norm, norm_params
-from .spec import ModelSpec, ParamDecl
+from .block import build_norm, norm_params, stream_options
+from .spec import ModelSpec, ParallelSpec, ParamDecl
 
 
 def block_owns_cache(spec: ModelSpec) -> List[bool]:
@@ -33,6 +33,10 @@ def param_decls(spec: ModelSpec) -> Dict[str, ParamDecl]:
         spec.embedding_name: ParamDecl((spec.vocab_size, spec.hidden), "embedding"),
     }
     out.update(norm_params(spec.final_norm, spec.final_norm_name))
+    if spec.embedding_norm is not None:
+        out.update(norm_params(*spec.embedding_norm))
+    for name, rows in added_rows(spec).items():
+        out[name] = ParamDecl((rows, spec.hidden), "bias")
     if spec.head_name is not None:
         out[spec.head_name] = ParamDecl((spec.vocab_size, spec.hidden), "linear")
     used = {call.layer for call in spec.order}
@@ -40,6 +44,18 @@ def param_decls(spec: ModelSpec) -> Dict[str, ParamDecl]:
         if i in used:
             out.update(arrangement_class(b.arrangement).params(b, owns))
     return out
+
+
+def added_rows(spec: ModelSpec) -> Dict[str, int]:
+    """{tensor name: rows} of the tensors whose rows calls of the run order add to the stream."""
+    rows: Dict[str, int] = {}
+    for call in spec.order:
+        if call.add is not None:
+            name, row = call.add
+            if row < 0:
+                raise ValueError(f"run order: row {row} of {name!r}")
+            rows[name] = max(rows.get(name, 0), row + 1)
+    return rows
 
 
 def validate_order(spec: ModelSpec) -> None:
@@ -62,6 +78,9 @@ def validate_order(spec: ModelSpec) -> None:
             if src.cache_of is not None:
                 raise ValueError(f"run order entry {pos} reads the cache of entry "
                                  f"{call.cache_of}, which owns none")
+            if any(isinstance(spec.layers[c.layer].mixer, ParallelSpec) for c in (call, src)):
+                raise ValueError(f"run order entry {pos}: a mixer of several mixers keeps "
+                                 f"caches of its own")
             a = mixer_class(spec.layers[call.layer].mixer.kind).cache_need(
                 spec.layers[call.layer].mixer)
             b = mixer_class(spec.layers[src.layer].mixer.kind).cache_need(
@@ -84,6 +103,14 @@ class Model:
         self.head = (tensors[spec.head_name].contiguous() if spec.head_name is not None
                      else self.embedding)
         self.final_norm = build_norm(spec.final_norm, spec.final_norm_name, tensors, ops, dtype)
+        self.embedding_norm = None
+        if spec.embedding_norm is not None:
+            self.embedding_norm = build_norm(*spec.embedding_norm, tensors, ops, dtype)
+            if not hasattr(self.embedding_norm, "norm_f32"):
+                raise ValueError(f"a {spec.embedding_norm[0].kind} norm cannot normalise the "
+                                 f"embedding rows in float32")
+        self.added = {name: tensors[name].to(torch.float32).contiguous()
+                      for name in added_rows(spec)}
         used = {call.layer for call in spec.order}
         self.blocks = [arrangement_class(b.arrangement)(b, tensors, ops, dtype)
                        if i in used else None for i, b in enumerate(spec.layers)]
@@ -112,8 +139,12 @@ class Model:
         n = ctx.n_tokens
         resid = torch.empty((n, self.spec.hidden), dtype=torch.float32, device=self.device)
         self.ops.embed(self.embedding, ctx.token_ids, resid, self.spec.embedding_scale)
+        if self.embedding_norm is not None:
+            resid = self.embedding_norm.norm_f32(resid)
         stream = Stream(resid, None)
         for call, cache in zip(self.spec.order, caches):
+            if call.add is not None:
+                stream.pending_add = self.added[call.add[0]][call.add[1]]
             stream = self.blocks[call.layer].forward(stream, ctx, cache)
         if ctx.logit_rows.shape[0] == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32,
@@ -125,7 +156,8 @@ class Model:
         else:
             normed = self.final_norm.add_norm(stream.resid, stream.pending, ctx,
                                               rows=ctx.logit_rows,
-                                              delta_norm=stream.pending_norm)
+                                              delta_norm=stream.pending_norm,
+                                              **stream_options(stream))
         logits = self.ops.linear(normed, self.head, out_dtype=torch.float32)
         if self.spec.logit_softcap:
             self.ops.softcap(logits, self.spec.logit_softcap)

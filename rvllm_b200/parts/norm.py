@@ -27,18 +27,45 @@ class RMSNorm(Norm):
         # bfloat16 file without loss.
         self.weight = tensors["weight"].to(torch.float32).contiguous()
 
-    def add_norm(self, resid, delta, ctx, rows=None, delta_norm=None):
+    def add_norm(self, resid, delta, ctx, rows=None, delta_norm=None, delta_scale=None, add=None):
+        """`delta_scale` float32 [size] multiplies the pending rows before they are added, `add`
+        float32 [size] is added to every row of the stream; both in the same kernel."""
         delta = self._normed_delta(delta, delta_norm, ctx)
         n = resid.shape[0] if rows is None else rows.shape[0]
         out = self.ops.new_rows(n, self.spec.size, self.dtype, resid.device)
-        self.ops.add_rmsnorm(resid, delta, self.weight, self.spec.eps, out, rows)
+        if delta_scale is None and add is None:
+            self.ops.add_rmsnorm(resid, delta, self.weight, self.spec.eps, out, rows)
+        else:
+            self.ops.add_rmsnorm(resid, delta, self.weight, self.spec.eps, out, rows,
+                                 delta_scale=delta_scale if delta is not None else None, add=add)
         return out
 
+    def norm_f32(self, x):
+        """The normalised float32 rows of float32 `x`: rows that go on as the residual stream."""
+        out = torch.empty_like(x)
+        self.ops.add_rmsnorm(None, x, self.weight, self.spec.eps, out, None)
+        return out
 
     def norm(self, x, ctx):
         out = self.ops.new_rows(x.shape[0], self.spec.size, self.dtype, x.device)
         self.ops.add_rmsnorm(None, x, self.weight, self.spec.eps, out, None)
         return out
+
+
+class ScalarRMSNorm(RMSNorm):
+    """RMSNorm whose weight is a single number for all coordinates (a tensor without
+    dimensions in the file): x / sqrt(mean(x^2) + eps) * g."""
+
+    @staticmethod
+    def params(spec: NormSpec):
+        return {"weight": ParamDecl((), "norm")}
+
+    def __init__(self, spec: NormSpec, tensors, ops, dtype):
+        self.spec = spec
+        self.ops = ops
+        self.dtype = dtype
+        g = tensors["weight"].to(torch.float32).reshape(1)
+        self.weight = g.expand(spec.size).contiguous()
 
 
 class LayerNorm(Norm):
@@ -81,4 +108,5 @@ class LayerNorm(Norm):
 
 
 register_norm("rmsnorm", RMSNorm)
+register_norm("rmsnorm_scalar", ScalarRMSNorm)
 register_norm("layernorm", LayerNorm)

@@ -94,6 +94,9 @@ class AttentionSpec(MixerSpec):
     value_mix: Optional[str] = None             # "source": this call's values are kept for the
                                                 # step; "mix": v <- (1 - l) v + l v_source with
                                                 # the learned scalar "vmix", before the cache
+    head_gate: bool = False                     # head j's result is multiplied by
+                                                # sigmoid(W_g x)_j, one number per head (tensor
+                                                # "g" [heads, hidden]), before the output product
 
 
 @dataclass(frozen=True)
@@ -107,6 +110,14 @@ class LatentAttentionSpec(MixerSpec):
     out_gate    the concatenated heads are multiplied by sigmoid(W_g x) before the output
                 product (tensor "g" [heads * v_head_dim, hidden])
     A call that reads another call's latent rows has no W_dkv.
+
+    q_rank      > 0: queries pass a latent of their own, c_q = rmsnorm(W_dq x) [q_rank] with
+                weight "dq_norm", q = W_uq c_q (tensors "dq", "dq_norm", "uq" instead of "q")
+    rot_dim     > 0: a head's query has `rot_dim` more dimensions after its `head_dim` plain
+                ones, W_dkv has `rot_dim` more rows after the latent's, and these parts are
+                turned by the position (rotate-half over the whole part, frequencies
+                rot_theta^(-2i/rot_dim)); the turned key part is shared by all heads, cached
+                beside the latent row, and the score is the sum of both parts' products
     """
     num_heads: int = 0
     head_dim: int = 0
@@ -117,6 +128,9 @@ class LatentAttentionSpec(MixerSpec):
     sinks: bool = False
     out_gate: bool = False
     names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    q_rank: int = 0
+    rot_dim: int = 0
+    rot_theta: float = 10000.0
 
 
 @dataclass(frozen=True)
@@ -168,6 +182,30 @@ class GatedDeltaSpec(MixerSpec):
 
 
 @dataclass(frozen=True)
+class MLSTMSpec(MixerSpec):
+    """The matrix memory with exponential gates (mLSTM): `num_heads` heads with keys and
+    queries of `head_dim` and values of `v_head_dim`; the pre-activations of the input and the
+    forget gate are capped as cap * tanh(. / cap) with `gate_cap`; `norm_eps` sits under the
+    root of the per-head norm of the read-out."""
+    num_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    gate_cap: float = 15.0
+    norm_eps: float = 1e-6
+    names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+
+
+@dataclass(frozen=True)
+class ParallelSpec(MixerSpec):
+    """Several mixers side by side that read the same input; the result is the sum of their
+    outputs, each times its factor.  `prefixes[j]` is where branch j's tensors lie below the
+    mixer's own prefix.  Every branch keeps a cache of its own."""
+    branches: Tuple[MixerSpec, ...] = ()
+    scales: Tuple[float, ...] = ()
+    prefixes: Tuple[str, ...] = ()
+
+
+@dataclass(frozen=True)
 class ShortConvSpec(MixerSpec):
     taps: int = 0                               # filter length; the state holds taps-1 rows
     bias: bool = False
@@ -188,7 +226,7 @@ class SwiGLUSpec(FeedForwardSpec):
 
 @dataclass(frozen=True)
 class DenseSpec(FeedForwardSpec):
-    """down(act(up(x))) with one of the registered activations."""
+    """down(act(up(x))) with one of the registered activations ("xielu", "relu2")."""
     ffn_dim: int = 0
     activation: str = "xielu"
     names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
@@ -217,7 +255,10 @@ class MoESpec(FeedForwardSpec):
     Options: score "softmax" (over all experts); `renormalize` false leaves the chosen scores
     undivided; `route_scale` multiplies every weight; `activation` "glu_clamp" gives the experts
     the clamped form of `GluClampSpec` with `limit` and `alpha`; `shared` is a feed-forward
-    that every token passes as well and whose output is added (tensors under "shared.")."""
+    that every token passes as well and whose output is added (tensors under "shared.");
+    `activation` "relu2": experts without a gate, down_e(max(up_e x, 0)^2); `choice_bias`: a
+    learned number per expert (tensor "correction" [experts]) is added to the scores where
+    experts are compared, while the weights are made from the scores without it."""
     ffn_dim: int = 0
     experts: int = 0
     top: int = 0
@@ -233,6 +274,7 @@ class MoESpec(FeedForwardSpec):
     alpha: float = 1.702
     shared: Optional[FeedForwardSpec] = None
     names: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    choice_bias: bool = False
 
 
 @dataclass(frozen=True)
@@ -249,6 +291,11 @@ class BlockSpec:
     neither).  The *_prefix fields say where the mixer's and the feed-forward's tensors
     are found in the file.
 
+    `layer_scale` maps the places "mixer" and "ffn" to a tensor [hidden] by which that
+    sub-layer's output is multiplied, channel by channel, before it is added, and
+    `residual_scale` multiplies every sub-layer's output ("pre_norm" blocks):
+        h = x + residual_scale * scale_mixer * mixer(...)
+
     "hyper_pre_norm" keeps `streams` >= 1 copies of the residual (hyper-connections); `hyper` maps
     the places "mixer" and "ffn" to the prefix of that sub-layer's three tensors (".in" [S],
     ".out" [S], ".mix" [S, S]).
@@ -261,15 +308,20 @@ class BlockSpec:
     ffn_prefix: str = ""
     streams: int = 0
     hyper: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    layer_scale: Mapping[str, str] = field(default_factory=dict, hash=False, compare=False)
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)
 class LayerCall:
     """One entry of the run order: run block `layer`; `cache_of`, if given, is the
     index (in the order list) of an earlier call whose cache this call reads instead of
-    owning one."""
+    owning one.  `add` = (tensor name, row): that row of a tensor [rows, hidden] is added to the
+    residual stream right before the call (what a repeated stretch of layers adds at the start
+    of each pass)."""
     layer: int
     cache_of: Optional[int] = None
+    add: Optional[Tuple[str, int]] = None
 
 
 @dataclass(frozen=True)
@@ -291,3 +343,5 @@ class ModelSpec:
                                                 # reads their sum
     bos_token_id: Optional[int] = None
     eos_token_id: Optional[int] = None
+    embedding_norm: Optional[Tuple[NormSpec, object]] = None   # (norm, tensor name): the
+                                                # embedding rows pass it before the first layer

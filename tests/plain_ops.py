@@ -29,17 +29,23 @@ class PlainOps:
         out.copy_(x if scale is None else x * scale)
 
     # ---- residual add + RMSNorm ------------------------------------------------------
-    def add_rmsnorm(self, resid, delta, weight, eps, out, rows=None):
+    def add_rmsnorm(self, resid, delta, weight, eps, out, rows=None, delta_scale=None, add=None):
+        if delta is not None and delta_scale is not None:
+            delta = _f(delta) * _f(delta_scale)
         if resid is None:
-            x = _f(delta)
+            x = _f(delta) if add is None else _f(delta) + _f(add)
         elif rows is None:
             if delta is not None:
                 resid.add_(_f(delta))
+            if add is not None:
+                resid.add_(_f(add))
             x = resid
         else:
             x = resid[rows.long()]
             if delta is not None:
                 x = x + _f(delta[rows.long()])
+            if add is not None:
+                x = x + _f(add)
         rms = (x.pow(2).mean(dim=-1, keepdim=True) + eps).sqrt()
         out.copy_((x / rms * _f(weight)).to(out.dtype))
 
@@ -290,7 +296,7 @@ class PlainOps:
             coef, every = q_temp
             steps = torch.div(positions.long() + 1, every, rounding_mode="floor") + 1
             q = q * (1.0 + coef * torch.log(steps.to(torch.float32)))[:, None, None]
-        rows[:, :H * d] = q.reshape(n, H * d).to(rows.dtype)
+        rows[:, :H * d] = q.reshape(n, H * d).to(rows.dtype).clone()
         if G:
             k = unit(_f(rows[:, H * d:(H + G) * d]).reshape(n, G, d))
             v = rows[:, (H + G) * d:(H + G) * d + G * dv].reshape(n, G, dv)
@@ -325,20 +331,20 @@ class PlainOps:
 
     # ---- mixture of experts ---------------------------------------------------------------
     def moe_select(self, logits, groups, keep, group_top, weight_eps, ids, weights,
-                   score="sigmoid", renormalize=True, route_scale=1.0):
+                   score="sigmoid", renormalize=True, route_scale=1.0, choice_bias=None):
         n, E = logits.shape
         top = ids.shape[1]
         size = E // groups
         for t in range(n):
             s = torch.sigmoid(_f(logits[t])) if score == "sigmoid" else \
                 torch.softmax(_f(logits[t]), dim=0)
-            allowed = s.clone()
+            allowed = s.clone() if choice_bias is None else s + _f(choice_bias)
             if groups > 1:
-                gs = s.reshape(groups, size).sort(dim=1, descending=True).values[:, :group_top].sum(1)
+                gs = allowed.reshape(groups, size).sort(dim=1, descending=True).values[:, :group_top].sum(1)
                 kept = torch.sort(gs, descending=True, stable=True).indices[:keep].tolist()
                 for g in range(groups):
                     if g not in kept:
-                        allowed[g * size:(g + 1) * size] = -1.0
+                        allowed[g * size:(g + 1) * size] = -3.0e38
             chosen = torch.sort(allowed, descending=True, stable=True).indices[:top]
             ids[t] = chosen.to(torch.int32)
             w = s[chosen] / (s[chosen].sum() + weight_eps) if renormalize else s[chosen]
@@ -359,7 +365,9 @@ class PlainOps:
             for k in range(top):
                 e = int(ids[t, k])
                 gu = _f(gate_up[e]) @ _f(x[t])               # gate and up rows alternate
-                if activation == "glu_clamp":
+                if activation == "relu2":                    # no gate: the up rows alone
+                    act = gu.clamp(min=0).pow(2).to(x.dtype)
+                elif activation == "glu_clamp":
                     g, u = gu[0::2].clamp(max=limit), gu[1::2].clamp(-limit, limit)
                     act = (g * torch.sigmoid(alpha * g) * (u + 1)).to(x.dtype)
                 else:
@@ -369,6 +377,93 @@ class PlainOps:
 
     def softcap(self, logits, cap):
         logits.copy_(cap * torch.tanh(logits / cap))
+
+    # ---- relu squared; a sum of two mixers ---------------------------------------------
+    def relu2(self, z, out):
+        out.copy_(_f(z).clamp(min=0).pow(2).to(out.dtype))
+
+    def weighted_sum(self, a, sa, b, sb, out):
+        out.copy_((sa * _f(a) + sb * _f(b)).to(out.dtype))
+
+    # ---- latent rows with a query latent and a turned key part ---------------------------
+    @staticmethod
+    def _turn(x, positions, freq):
+        """x [n, ..., rot]: dimension i with i + rot/2 by the angle position * freq[i]."""
+        half = x.shape[-1] // 2
+        ang = positions.to(torch.float32)[:, None] * _f(freq)[None, :]
+        shape = (x.shape[0],) + (1,) * (x.dim() - 2) + (half,)
+        cos, sin = torch.cos(ang).reshape(shape), torch.sin(ang).reshape(shape)
+        u, v = x[..., :half], x[..., half:]
+        return torch.cat([u * cos - v * sin, v * cos + u * sin], dim=-1)
+
+    def latent_prepare(self, rows, q_off, q_rank, q_weight, cq, kv_off, rank, rot, kv_weight, eps,
+                       freq, positions, slot_mapping, cache):
+        def norm(x, w):
+            return x / (x.pow(2).mean(dim=-1, keepdim=True) + eps).sqrt() * _f(w)
+        if q_rank:
+            cq.copy_(norm(_f(rows[:, q_off:q_off + q_rank]), q_weight).to(cq.dtype))
+        c = norm(_f(rows[:, kv_off:kv_off + rank]), kv_weight)
+        if rot:
+            turned = self._turn(_f(rows[:, kv_off + rank:kv_off + rank + rot]), positions, freq)
+            c = torch.cat([c, turned], dim=-1)
+        pages = cache.view(-1, rank + rot)
+        for t in range(rows.shape[0]):
+            s = int(slot_mapping[t])
+            if s >= 0:
+                pages[s] = c[t].to(pages.dtype)
+
+    def rope_heads(self, x, heads, size, off, rot, freq, positions):
+        if not rot:
+            return
+        n = x.shape[0]
+        v = x[:, :heads * size].reshape(n, heads, size)
+        turned = self._turn(_f(v[..., off:off + rot]), positions, freq)
+        v[..., off:off + rot] = turned.to(x.dtype)
+        x[:, :heads * size] = v.reshape(n, heads * size)
+
+    def head_gate(self, x, heads, size, rows, gate_off):
+        g = torch.sigmoid(_f(rows[:, gate_off:gate_off + heads]))
+        y = _f(x).reshape(-1, heads, size) * g[:, :, None]
+        x.copy_(y.reshape(x.shape).to(x.dtype))
+
+    # ---- matrix memory with exponential gates ----------------------------------------------
+    def mlstm_record(self, heads, dim, vdim):
+        return heads * (vdim + 1) * dim + heads
+
+    def mlstm(self, rows, in_bias, forget_bias, norm_w, state, ctx, out, heads, dim, vdim, cap, eps):
+        H, d, dv = heads, dim, vdim
+        q_start = ctx.q_start.tolist()
+        slots = ctx.state_slot.tolist()
+        p = _f(rows)
+        o_q, o_k, o_v = 0, H * d, 2 * H * d
+        o_i = o_v + H * dv
+        o_f, o_g = o_i + H, o_i + 2 * H
+        for r in range(ctx.n_reqs):
+            a, b = q_start[r], q_start[r + 1]
+            if slots[r] < 0 or a == b:
+                continue
+            rec = state[slots[r]]
+            C = rec[:H * (dv + 1) * d].reshape(H, dv + 1, d).clone()      # a column's rows side by side
+            mx = rec[H * (dv + 1) * d:].clone()
+            for t in range(a, b):
+                li = cap * torch.tanh((p[t, o_i:o_i + H] + _f(in_bias)) / cap)
+                lf = torch.nn.functional.logsigmoid(
+                    cap * torch.tanh((p[t, o_f:o_f + H] + _f(forget_bias)) / cap))
+                new = torch.maximum(lf + mx, li)
+                keep, take = torch.exp(lf + mx - new), torch.exp(li - new)
+                mx = new
+                q = p[t, o_q:o_q + H * d].reshape(H, d) / math.sqrt(d)
+                k = p[t, o_k:o_k + H * d].reshape(H, d)
+                v = torch.cat([p[t, o_v:o_v + H * dv].reshape(H, dv), torch.ones(H, 1)], dim=1)
+                C = keep[:, None, None] * C + take[:, None, None] * v[:, :, None] * k[:, None, :]
+                read = torch.einsum("hcd,hd->hc", C, q)                   # [H, dv + 1]
+                den = torch.maximum(read[:, dv].abs(), torch.exp(-mx)) + 1e-6
+                o = read[:, :dv] / den[:, None]
+                o = o / (o.pow(2).mean(dim=-1, keepdim=True) + eps).sqrt()
+                gate = torch.sigmoid(p[t, o_g:o_g + H * dv])
+                out[t] = (o.reshape(H * dv) * _f(norm_w) * gate).to(out.dtype)
+            rec[:H * (dv + 1) * d] = C.reshape(-1)
+            rec[H * (dv + 1) * d:] = mx
 
     # ---- hyper-connections -----------------------------------------------------------
     def hyper_norm(self, src, dst, delta, mix, out_w, in_w, weight, eps, out, rows=None):
