@@ -38,6 +38,10 @@ attention with sinks, a mixture of experts) beside an all-attention LFM2 of equa
 `--only vifanex` (not part of the default run) measures Vifanex (gated delta rule and windowed
 attention in turn on several residual streams, a softmax-routed mixture with a shared expert)
 beside Bizenex at equal sizes.
+`--only mevuvik` (not part of the default run) measures Mevuvik (latent attention with a query
+latent and a turned shared key part, and a gated grouped-query attention beside a matrix memory
+with exponential gates, in turn; relu-squared dense and routed feed-forwards; a stretch of layers
+run twice) beside Bizenex with as many layer runs at equal sizes.
 `--only retorax` (not part of the default run) measures another design, Retorax, beside LFM2
 at equal sizes (width 1024 and 2048, eight layers): a 2,048-token prompt, single tokens at
 batch 8 and 64, and the device time of every kernel of a step against its roofline.
@@ -922,6 +926,41 @@ def vifanex_config(sz):
             "layers": layers}
 
 
+MEVUVIK_SIZES = {
+    # latent attention and (gated grouped-query attention beside a matrix memory) in turn; six
+    # layers of which the middle two run twice: eight layer runs, as many as Bizenex has layers.
+    # A latent row and its turned part fill a head of `rank` values, as Bizenex's latent rows do.
+    # The fields Bizenex reads are here too, so that it runs beside at equal sizes.
+    "w1024": {"width": 1024, "layers": 8, "heads": 16, "kv": 4, "dim": 64, "rank": 128, "rot": 16,
+              "q_rank": 256, "mem_heads": 8, "mem_dim": 64, "mem_vdim": 128,
+              "experts": 16, "top": 4, "groups": (4, 2), "ff": 1024, "vocab": 32768},
+    "w2048": {"width": 2048, "layers": 8, "heads": 32, "kv": 8, "dim": 64, "rank": 128, "rot": 16,
+              "q_rank": 512, "mem_heads": 16, "mem_dim": 64, "mem_vdim": 128,
+              "experts": 16, "top": 4, "groups": (4, 2), "ff": 2048, "vocab": 32768},
+}
+
+
+def mevuvik_config(sz):
+    moe = {"kind": "moe", "expert": {"ff": sz["ff"]},
+           "router": {"experts": sz["experts"], "top": sz["top"], "scale": 2.5}}
+    latent = {"heads": sz["heads"], "dim": sz["dim"], "rot_dim": sz["rot"], "vdim": sz["dim"],
+              "kv_rank": sz["rank"] - sz["rot"], "q_rank": sz["q_rank"],
+              "scale": (sz["dim"] + sz["rot"]) ** -0.5, "rot": {"base": 10000.0, "dims": sz["rot"]}}
+    par = {"left": {"heads": sz["heads"], "kv_heads": sz["kv"], "dim": sz["dim"], "vdim": sz["dim"],
+                    "scale": sz["dim"] ** -0.5},
+           "right": {"heads": sz["mem_heads"], "dim": sz["mem_dim"], "vdim": sz["mem_vdim"],
+                     "gate_cap": 15.0},
+           "left_scale": 1.0, "right_scale": 1.0}
+    layers = []
+    for i in range(sz["layers"] - 2):
+        mlp = {"kind": "dense", "ff": sz["top"] * sz["ff"]} if i == 0 else moe
+        layers.append({"type": "latent_attention", "mixer": latent, "mlp": mlp} if i % 2 == 0 else
+                      {"type": "parallel", "mixer": par, "mlp": mlp})
+    return {"architecture": "Mevuvik", "vocab": sz["vocab"], "width": sz["width"],
+            "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_softcap": 30.0,
+            "loop": {"start": 2, "stop": 4, "times": 2}, "layers": layers}
+
+
 def lfm2_all_attention(sz):
     """LFM2 with the same width and layer count, attention in every layer with the same head
     counts and sizes, and a SwiGLU as wide as the experts a token uses together."""
@@ -951,7 +990,8 @@ class OpTimer:
              "qk_norm_rope_write", "rope_partial_write", "paged_attention", "paged_attention_mixed",
              "short_conv", "mingru_scan", "swiglu", "xielu", "qk_unit_write", "latent_norm_write",
              "heads_product", "sigmoid_gate", "moe_select", "moe_route", "moe_experts", "softcap",
-             "hyper_norm", "qkv_full_norm_rope_write", "gated_delta", "glu_clamp")
+             "hyper_norm", "qkv_full_norm_rope_write", "gated_delta", "glu_clamp", "relu2",
+             "weighted_sum", "latent_prepare", "rope_heads", "head_gate", "mlstm")
 
     def __init__(self, torch, ops):
         self.torch, self.ops, self.events, self.saved = torch, ops, [], {}
@@ -988,7 +1028,7 @@ class OpTimer:
 
 
 def run_designs(args, which="retorax"):
-    """Retorax (`--only retorax`) or Bizenex (`--only bizenex`) beside LFM2, or Vifanex
+    """Retorax (`--only retorax`) or Bizenex (`--only bizenex`) beside LFM2, Mevuvik (`--only mevuvik`) beside Bizenex, or Vifanex
     (`--only vifanex`) beside Bizenex, at equal sizes:
     prompt and single-token throughput, and the device time of every kernel of one prompt step
     and one single-token step with its share of the roofline.  One JSON line."""
@@ -1004,7 +1044,8 @@ def run_designs(args, which="retorax"):
     T, CTX = 2048, 1024
     sampler = ClockSampler()
     sampler.start()
-    sizes = {"retorax": RETORAX_SIZES, "bizenex": BIZENEX_SIZES, "vifanex": VIFANEX_SIZES}[which]
+    sizes = {"retorax": RETORAX_SIZES, "bizenex": BIZENEX_SIZES, "vifanex": VIFANEX_SIZES,
+             "mevuvik": MEVUVIK_SIZES}[which]
     for size_name, sz in sizes.items():
         if args.design_size not in ("all", size_name):
             continue
@@ -1013,6 +1054,8 @@ def run_designs(args, which="retorax"):
             pair = (("retorax", retorax_config(sz)), ("lfm2", lfm2_like(sz)))
         elif which == "bizenex":
             pair = (("bizenex", bizenex_config(sz)), ("lfm2", lfm2_all_attention(sz)))
+        elif which == "mevuvik":
+            pair = (("mevuvik", mevuvik_config(sz)), ("bizenex", bizenex_config(sz)))
         else:
             pair = (("vifanex", vifanex_config(sz)), ("bizenex", bizenex_config(sz)))
         for design, data in pair:
@@ -1085,7 +1128,8 @@ def run_designs(args, which="retorax"):
             del model
             torch.cuda.empty_cache()
         entry["rooflines"] = {"retorax": design_rooflines, "bizenex": bizenex_rooflines,
-                              "vifanex": vifanex_rooflines}[which](sz, entry, pk, T, CTX)
+                              "vifanex": vifanex_rooflines,
+                              "mevuvik": mevuvik_rooflines}[which](sz, entry, pk, T, CTX)
         out[size_name] = entry
     out["clocks"] = sampler.stop()
     print(json.dumps(out))
@@ -1255,6 +1299,78 @@ def vifanex_rooflines(sz, entry, pk, T, CTX):
     return rows
 
 
+def mevuvik_rooflines(sz, entry, pk, T, CTX):
+    """Per kernel pair (Mevuvik's kernel, Bizenex's like kernel): device time of all calls in the
+    prompt step, and the time the roofline allows: bytes / measured copy rate for the elementwise
+    kernels, tensor FLOPs / measured GEMM rate for attention and the experts' products, and for
+    the matrix memory its float32 FLOPs (5 a state element a token: the decay, the write, the
+    read-out) on the CUDA cores at their nominal rate.  The memory has no like kernel in Bizenex."""
+    W, F, H, G, D, R = sz["width"], sz["ff"], sz["heads"], sz["kv"], sz["dim"], sz["rank"]
+    E, top, rot, Rq = sz["experts"], sz["top"], sz["rot"], sz["q_rank"]
+    Hm, Dm, Vm = sz["mem_heads"], sz["mem_dim"], sz["mem_vdim"]
+    runs = sz["layers"]                              # layer runs of both designs
+    n_lat = n_par = runs // 2                        # Mevuvik: latent runs and parallel runs
+    n_moe = runs - 1                                 # its first feed-forward is dense
+    hbm = pk["hbm_gbs"] * 1e3                        # bytes per microsecond
+    tens = pk["bf16_tflops"] * 1e6                   # FLOPs per microsecond
+    fp32 = FP32_TFLOPS_NOMINAL * 1e6
+    pairs = T * (T + 1) // 2
+    mem_cols = 2 * Hm * Dm + 2 * Hm * Vm + 2 * Hm    # q, k, v, two gates, the output gate
+    ideal = {
+        # the stream read and written, the pending rows and the scale read, the normed rows written
+        "add_rmsnorm": (2 * runs + 2) * T * W * (4 + 4 + 2 + 2) / hbm,
+        "add_layernorm": (2 * runs + 1) * T * W * (4 + 4 + 2 + 2) / hbm,
+        # both latents read, the query latent and the page slot written
+        "latent_prepare": n_lat * T * (Rq + R) * 4 / hbm,
+        "latent_norm_write": ((runs + 1) // 2 + 1) // 2 * T * R * 4 / hbm,
+        "rope_heads": n_lat * T * H * rot * 4 / hbm,
+        "paged_attention": (n_lat * pairs * 4.0 * H * R + n_par * pairs * 4.0 * H * D) / tens,
+        "paged_attention_bizenex": ((runs + 1) // 2 * pairs * 4.0 * H * R + runs // 2 * pairs * 4.0 * H * D) / tens,
+        "qk_unit_write": n_par * T * ((H + 2 * G) * D * 2 + 2 * G * D * 2) / hbm,
+        "qk_unit_write_bizenex": runs // 2 * T * ((H + G) * D * 4 + 2 * G * D * 2) / hbm,
+        "head_gate": n_par * T * H * D * 4 / hbm,
+        "weighted_sum": n_par * T * W * 6 / hbm,
+        "sigmoid_gate": (runs + 1) // 2 * T * H * D * 6 / hbm,
+        "relu2": T * top * F * 4 / hbm,
+        "moe_route": n_moe * T * (W * 2 + top * 8) / hbm,
+        "moe_route_bizenex": runs * T * (W * 2 + top * 8) / hbm,
+        "moe_experts": n_moe * T * top * 4.0 * F * W / tens,
+        "moe_experts_bizenex": runs * T * top * 6.0 * F * W / tens,
+        "mlstm": n_par * max(T * Hm * 5.0 * Dm * (Vm + 1) / fp32,
+                             T * (mem_cols * 4 + Hm * Vm * 2) / hbm),
+    }
+    ours, theirs = entry["mevuvik"]["prefill_2048_kernels_us"], entry["bizenex"]["prefill_2048_kernels_us"]
+    like = (("add_rmsnorm", "add_layernorm", "add_layernorm"),
+            ("latent_prepare", "latent_norm_write", "latent_norm_write"),
+            ("rope_heads", "latent_norm_write", "latent_norm_write"),
+            ("paged_attention", "paged_attention", "paged_attention_bizenex"),
+            ("qk_unit_write", "qk_unit_write", "qk_unit_write_bizenex"),
+            ("head_gate", "sigmoid_gate", "sigmoid_gate"),
+            ("weighted_sum", "sigmoid_gate", "sigmoid_gate"),
+            ("relu2", "sigmoid_gate", "sigmoid_gate"),
+            ("moe_route", "moe_route", "moe_route_bizenex"),
+            ("moe_experts", "moe_experts", "moe_experts_bizenex"),
+            ("mlstm", None, None))
+    rows = {}
+    for mine, other, other_ideal in like:
+        a, b = ours.get(mine), theirs.get(other) if other else None
+        if not a:
+            continue
+        rows[mine] = {"us": a["us"], "calls": a["calls"], "roofline_us": round(ideal[mine], 1),
+                      "times_roofline": round(a["us"] / ideal[mine], 2)}
+        if b:
+            rows[mine].update({"like": other, "like_us": b["us"],
+                               "like_roofline_us": round(ideal[other_ideal], 1),
+                               "like_times_roofline": round(b["us"] / ideal[other_ideal], 2)})
+    # single tokens at batch 64: the state of every request is read and written once a layer run
+    dec = entry["mevuvik"].get("decode_b64_kernels_us", {}).get("mlstm")
+    if dec:
+        state_bytes = n_par * 64 * 2.0 * Hm * Dm * (Vm + 1) * 4
+        rows["mlstm_decode_b64"] = {"us": dec["us"], "roofline_us": round(state_bytes / hbm, 1),
+                                    "times_roofline": round(dec["us"] / (state_bytes / hbm), 2)}
+    return rows
+
+
 def run_reference(args):
     print(json.dumps({
         "impl": "reference",
@@ -1272,14 +1388,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", default="1.2b", choices=sorted(SIZES),
                     help="layer sizes: LFM2-1.2B (the default and the headline), 700M or 350M")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload", "further", "retorax", "bizenex", "vifanex"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels", "breakdown", "workload", "further", "retorax", "bizenex", "vifanex", "mevuvik"],
                     help="run one part only (for profiling); the JSON line then lacks the rest")
     ap.add_argument("--workloads", default="both", choices=["both", "none"] + sorted(WORKLOADS),
                     help="scheduler workloads to add to the line (default: both)")
     ap.add_argument("--workload", default="350m-mixed", choices=sorted(WORKLOADS),
                     help="with --only workload: which one")
     ap.add_argument("--design-size", default="all", choices=["all"] + sorted(set(RETORAX_SIZES) | set(VIFANEX_SIZES)),
-                    help="with --only retorax, bizenex or vifanex: which of the sizes")
+                    help="with --only retorax, bizenex, vifanex or mevuvik: which of the sizes")
     ap.add_argument("--kernel", default="all",
                     help="with --only kernels: attn_decode, attn_prefill, gemm, gemm:NxK, elementwise, copy_rate or all")
     ap.add_argument("--kernel-batch", type=int, default=64)
@@ -1308,6 +1424,8 @@ def main():
         return run_designs(args, "bizenex")
     if args.only == "vifanex":
         return run_designs(args, "vifanex")
+    if args.only == "mevuvik":
+        return run_designs(args, "mevuvik")
     if args.only == "workload":
         print(json.dumps({"only": "workload", args.workload: run_workload(args.workload)}))
         return 0

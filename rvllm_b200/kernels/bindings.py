@@ -489,7 +489,10 @@ class CudaOps:
                 raise KernelError("paged_attention: one sink per query head")
         if out.shape[1] != num_heads * vd:
             raise KernelError("paged_attention: output width and head sizes disagree")
-        mma = self._mma_ok(qkv.dtype, head_dim)
+        # the tensor-core kernels fetch query rows in 16-byte pieces: rows of another stride or
+        # start take the float32-arithmetic kernels
+        mma = (self._mma_ok(qkv.dtype, head_dim) and qkv.shape[1] % 8 == 0
+               and qkv.data_ptr() % 16 == 0)
         if vd != head_dim or (sinks is not None and not mma):
             # a value size of its own, or sinks where no tensor-core kernel applies: the
             # float32-arithmetic kernels

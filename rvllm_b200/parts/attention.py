@@ -131,15 +131,28 @@ class Attention(Mixer):
         n = self._names(spec)
         q = tensors[n["q_proj"]]
         self.has_kv = n["k_proj"] in tensors
-        gate = [tensors[n["head_gate"]].to(q.dtype)] if spec.head_gate else []
+        def fused(parts):
+            """The matrices as one; with gate rows at the end, zero rows after them fill the
+            product's width up to a multiple of the head size (of 8 at least), so that the rows
+            keep the alignment and the shape that the tensor-core attention kernels read."""
+            if not spec.head_gate:
+                return torch.cat(parts, dim=0).contiguous()
+            parts = parts + [tensors[n["head_gate"]].to(q.dtype)]
+            rows = sum(p.shape[0] for p in parts)
+            unit = spec.head_dim if spec.head_dim % 8 == 0 else 8
+            fill = -rows % unit
+            if fill:
+                parts.append(torch.zeros((fill, spec.hidden), dtype=q.dtype, device=q.device))
+            return torch.cat(parts, dim=0).contiguous()
+
         if self.has_kv:
-            self.w_qkv = torch.cat([q, tensors[n["k_proj"]].to(q.dtype),
-                                    tensors[n["v_proj"]].to(q.dtype)] + gate, dim=0).contiguous()
+            self.w_qkv = fused([q, tensors[n["k_proj"]].to(q.dtype),
+                                tensors[n["v_proj"]].to(q.dtype)])
         else:
-            self.w_qkv = torch.cat([q] + gate, dim=0).contiguous()
+            self.w_qkv = fused([q])
         # a call that reads another call's pages multiplies q (and the gate) only
-        self.w_q = self.w_qkv[:spec.num_heads * spec.head_dim] if not gate else \
-            torch.cat([q] + gate, dim=0).contiguous()
+        self.w_q = self.w_qkv[:spec.num_heads * spec.head_dim] if not spec.head_gate else \
+            fused([q])
         self.w_out = tensors[n["out_proj"]].contiguous()
         self.q_norm = self.k_norm = None
         self.v_dim = spec.v_head_dim or spec.head_dim
@@ -208,7 +221,7 @@ class Attention(Mixer):
                                  sinks=self.sinks, v_head_dim=self.v_dim)
         if s.head_gate:
             self.ops.head_gate(out, s.num_heads, self.v_dim, rows,
-                               rows.shape[1] - s.num_heads)
+                               s.num_heads * s.head_dim + kv * (s.head_dim + self.v_dim))
         return self.ops.linear(out, self.w_out, out_dtype=self.dtype)
 
 
