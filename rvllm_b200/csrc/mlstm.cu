@@ -223,15 +223,18 @@ extern "C" int rv_mlstm(const float* rows, int stride, const float* bi, const fl
     const size_t smem = (size_t)(2 * ML_TC * P * R + ML_TC * CPB + 2 * ML_TC) * sizeof(float);
     const float q_scale = 1.f / sqrtf((float)d);
 #define ML_SCAN(RR)                                                                               \
-    if (smem > 48 * 1024 &&                                                                       \
-        cudaFuncSetAttribute(mlstm_scan_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                             (int)smem) != cudaSuccess)                                           \
-        RV_FAIL("mlstm: %zu bytes of shared memory are not to be had", smem);                     \
-    rv_launch(mlstm_scan_kernel<RR>, grid, dim3(ML_THREADS), smem, s, rows, stride, H, d, dv, P,  \
-              q_start, state_slot, state, rec, (const float*)gate, num, q_scale)
-    if (R == 4) ML_SCAN(4);
-    else if (R == 8) ML_SCAN(8);
-    else ML_SCAN(16);
+    {                                                                                             \
+        if (smem > 48 * 1024 &&                                                                   \
+            cudaFuncSetAttribute(mlstm_scan_kernel<RR>,                                           \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,                     \
+                                 (int)smem) != cudaSuccess)                                       \
+            RV_FAIL("mlstm: %zu bytes of shared memory are not to be had", smem);                 \
+        rv_launch(mlstm_scan_kernel<RR>, grid, dim3(ML_THREADS), smem, s, rows, stride, H, d, dv, \
+                  P, q_start, state_slot, state, rec, (const float*)gate, num, q_scale);          \
+    }
+    if (R == 4) ML_SCAN(4)
+    else if (R == 8) ML_SCAN(8)
+    else ML_SCAN(16)
 #undef ML_SCAN
     RV_CHECK_LAUNCH("mlstm_scan");
     const long long warps = (long long)n_tokens * H;
