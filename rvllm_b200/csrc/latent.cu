@@ -249,12 +249,40 @@ extern "C" int rv_rope_heads(void* x, int dtype, int row_stride, int n_tokens, i
     return 0;
 }
 
+// eight bfloat16 values a thread (all of one head), 16-byte accesses
+__global__ void head_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ x, int width8, int size8,
+                                        const __nv_bfloat16* __restrict__ rows, int row_stride,
+                                        int gate_off, long long total8) {
+    rv_pdl_prologue();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const long long n = i / width8;
+    const int h = (int)(i - n * width8) / size8;
+    const float den = 1.f + expf(-__bfloat162float(rows[n * row_stride + gate_off + h]));
+    uint4 xv = *(const uint4*)(x + i * 8);
+    __nv_bfloat162* xp = (__nv_bfloat162*)&xv;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 a = __bfloat1622float2(xp[j]);
+        xp[j] = __floats2bfloat162_rn(a.x / den, a.y / den);
+    }
+    *(uint4*)(x + i * 8) = xv;
+}
+
 extern "C" int rv_head_gate(void* x, int dtype, int n, int heads, int size, const void* rows,
                             int row_stride, int gate_off, void* stream) {
     if (n == 0) return 0;
     if (n < 0 || heads <= 0 || size <= 0 || gate_off < 0 || row_stride < gate_off + heads)
         RV_FAIL("head_gate: bad sizes");
     const long long total = (long long)n * heads * size;
+    if (dtype == RV_DTYPE_BF16 && size % 8 == 0 && ((uintptr_t)x & 15) == 0) {
+        const long long total8 = total / 8;
+        rv_launch(head_gate_bf16x8_kernel, dim3((unsigned)((total8 + 255) / 256)), dim3(256), 0,
+                  (cudaStream_t)stream, (__nv_bfloat16*)x, heads * size / 8, size / 8,
+                  (const __nv_bfloat16*)rows, row_stride, gate_off, total8);
+        RV_CHECK_LAUNCH("head_gate");
+        return 0;
+    }
     const long long blocks = (total + 255) / 256;
     if (blocks > 0x7fffffffLL) RV_FAIL("head_gate: too many values");
     RV_DISPATCH_DTYPE(dtype, "head_gate",

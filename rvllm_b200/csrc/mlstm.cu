@@ -20,11 +20,12 @@
 //           exp(-m) of all tokens in parallel -> gate [N, H, 4]; the record's maximum moves on.
 //   scan    block per (tile of columns, head, request): P neighbouring lanes share a column and
 //           each holds R of its rows in registers for the whole portion; q, k, v and the gates
-//           of sixteen tokens at a time are staged in shared memory; per token every lane does
-//           R multiply-adds into its rows and R into its part of the column's sum, which P
-//           lanes add by shuffles -> num [N, H, dv + 1].  A column never meets another, so the
-//           columns of a head are spread over blocks, and a token's sums are formed in the same
-//           order however its prompt was cut.
+//           of sixteen tokens at a time arrive in a ring of shared-memory buffers by cp.async
+//           while the sixteen before them are worked on; per token every lane does R
+//           multiply-adds into its rows and R into its part of the column's sum; the sums of
+//           sixteen tokens are added over the P lanes together -> num [N, H, dv + 1].  A
+//           column never meets another, so the columns of a head are spread over blocks, and a
+//           row's sums are formed token after token in the same order however a prompt was cut.
 //   finish  warp per (token, head): the division, the head's norm, weight and gate.
 // Plain reference: tests/plain_ops.py mlstm.
 #include "common.cuh"
@@ -61,8 +62,24 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_gates_kernel(
         }
         __syncthreads();
         if (threadIdx.x == 0) {
+            // the one chain of the layer: an add and a max a token, eight tokens' gates fetched
+            // before the eight links that use them
             float m = ms[0];
-            for (int t = 0; t < n; ++t) {
+            int t = 0;
+            for (; t + 8 <= n; t += 8) {
+                float gi[8], gf[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    gi[u] = li[t + u];
+                    gf[u] = lf[t + u];
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    m = fmaxf(gf[u] + m, gi[u]);
+                    ms[t + u + 1] = m;
+                }
+            }
+            for (; t < n; ++t) {
                 m = fmaxf(lf[t] + m, li[t]);
                 ms[t + 1] = m;
             }
@@ -80,67 +97,205 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_gates_kernel(
     if (threadIdx.x == 0) *m_rec = ms[0];
 }
 
+__device__ __forceinline__ void ml_cp4(float* smem, const float* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(
+                     (unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void ml_cp8(float* smem, const float* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(
+                     (unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+__device__ __forceinline__ void ml_cp16(float* smem, const float* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(
+                     (unsigned)__cvta_generic_to_shared(smem)), "l"(gmem));
+}
+
 // P lanes a column, R rows a lane: P * R >= d.  Rows beyond d are zeros and stay zeros.
+// Sixteen tokens at a time lie in one of `nb` shared-memory buffers; the chunks after them are
+// requested (cp.async, 16 bytes a piece where `vec` says the rows allow it) before these are
+// worked on.  Only a row's own multiply-add links one token to the next: the column sums of
+// sixteen tokens are kept in registers and added over the P lanes afterwards, sixteen
+// independent shuffles a round, and the query's factor d^(-1/2) multiplies the finished sum.
 template <int R>
 __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
     const float* __restrict__ rows, int stride, int H, int d, int dv, int P,
     const int* __restrict__ q_start, const int* __restrict__ state_slot, float* __restrict__ state,
-    long long rec, const float* __restrict__ gate, float* __restrict__ num, float q_scale) {
+    long long rec, const float* __restrict__ gate, float* __restrict__ num, float q_scale, int vec,
+    int nb) {
     rv_pdl_launch_dependents();
     const int h = blockIdx.y, r = blockIdx.z;
     const int slot = state_slot[r];
     const int a0 = q_start[r], a1 = q_start[r + 1];
-    rv_pdl_wait();
-    if (slot < 0 || a1 <= a0) return;
     extern __shared__ __align__(16) float sm[];
     const int DP = P * R;                        // padded rows
     const int CPB = ML_THREADS / P;              // columns a block
-    float* qs = sm;                              // [ML_TC][DP]
-    float* ks = qs + ML_TC * DP;                 // [ML_TC][DP]
-    float* vs = ks + ML_TC * DP;                 // [ML_TC][CPB]
-    float* gs = vs + ML_TC * CPB;                // [ML_TC][2]
+    const int stage = 2 * ML_TC * DP + ML_TC * CPB + 2 * ML_TC;      // a multiple of 4 floats
     const int tid = threadIdx.x;
     const int part = tid % P, cl = tid / P;
     const int col = blockIdx.x * CPB + cl;       // dv: the column of n
     const bool live = col <= dv;
     const int r0 = part * R;
+    if (slot < 0 || a1 <= a0) {
+        rv_pdl_wait();
+        return;
+    }
+    if (a1 - a0 == 1) {
+        // a single token: nothing is staged; every lane reads its rows of the column, its
+        // stretch of k and q, and forms the same sums in the same order as below
+        rv_pdl_wait();
+        const float* row = rows + (size_t)a0 * stride;
+        const float* gt = gate + ((size_t)a0 * H + h) * 4;
+        const float a = gt[0];
+        const float bv = gt[1] * ((live && col < dv) ? row[2 * H * d + h * dv + col] : 1.f);
+        float* cr = state + (size_t)slot * rec + ((size_t)h * (dv + 1) + col) * d;
+        const float* kr = row + H * d + h * d;
+        const float* qr = row + h * d;
+        float sum = 0.f;
+        if (vec & 2) {
+#pragma unroll
+            for (int j = 0; j < R; j += 4) {
+                if (live && r0 + j < d) {
+                    float4 s4 = *(const float4*)(cr + r0 + j);
+                    const float4 k4 = *(const float4*)(kr + r0 + j), q4 = *(const float4*)(qr + r0 + j);
+                    s4.x = fmaf(a, s4.x, bv * k4.x);
+                    s4.y = fmaf(a, s4.y, bv * k4.y);
+                    s4.z = fmaf(a, s4.z, bv * k4.z);
+                    s4.w = fmaf(a, s4.w, bv * k4.w);
+                    sum = fmaf(s4.x, q4.x, sum);
+                    sum = fmaf(s4.y, q4.y, sum);
+                    sum = fmaf(s4.z, q4.z, sum);
+                    sum = fmaf(s4.w, q4.w, sum);
+                    *(float4*)(cr + r0 + j) = s4;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < R; ++j) {
+                if (live && r0 + j < d) {
+                    const float sj = fmaf(a, cr[r0 + j], bv * kr[r0 + j]);
+                    sum = fmaf(sj, qr[r0 + j], sum);
+                    cr[r0 + j] = sj;
+                }
+            }
+        }
+        for (int o = P >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (part == 0 && live) num[((size_t)a0 * H + h) * (dv + 1) + col] = sum * q_scale;
+        return;
+    }
+    // zeros where no copy ever writes (rows beyond d, columns beyond dv); ones as the values of
+    // the column of n
+    for (int i = tid; i < nb * stage; i += ML_THREADS) {
+        const int x = i % stage - 2 * ML_TC * DP;
+        const bool n_col = x >= 0 && x < ML_TC * CPB && blockIdx.x * CPB + x % CPB == dv;
+        sm[i] = n_col ? 1.f : 0.f;
+    }
+    rv_pdl_wait();
     float S[R];
     float* col_rec = state + (size_t)slot * rec + ((size_t)h * (dv + 1) + col) * d;
 #pragma unroll
     for (int j = 0; j < R; ++j) S[j] = (live && r0 + j < d) ? col_rec[r0 + j] : 0.f;
     const int q_off = h * d, k_off = H * d + h * d, v_off = 2 * H * d + h * dv;
     const int W = dv + 1;
-    for (int c0 = a0; c0 < a1; c0 += ML_TC) {
+    __syncthreads();                             // the buffers are set before any copy lands
+    auto request = [&](int c0, float* buf) {
         const int n = min(ML_TC, a1 - c0);
-        __syncthreads();                         // the previous chunk has been used
-        for (int i = tid; i < n * DP; i += ML_THREADS) {
-            const int t = i / DP, x = i - t * DP;
-            const float* row = rows + (size_t)(c0 + t) * stride;
-            qs[i] = x < d ? row[q_off + x] * q_scale : 0.f;
-            ks[i] = x < d ? row[k_off + x] : 0.f;
+        float* qs = buf;
+        float* ks = buf + ML_TC * DP;
+        float* vs = ks + ML_TC * DP;
+        float* gs = vs + ML_TC * CPB;
+        if (vec & 1) {
+            const int d4 = d >> 2;
+            for (int i = tid; i < n * d4; i += ML_THREADS) {
+                const int t = i / d4, x = (i - t * d4) << 2;
+                const float* row = rows + (size_t)(c0 + t) * stride;
+                ml_cp16(qs + t * DP + x, row + q_off + x);
+                ml_cp16(ks + t * DP + x, row + k_off + x);
+            }
+        } else {
+            for (int i = tid; i < n * d; i += ML_THREADS) {
+                const int t = i / d, x = i - t * d;
+                const float* row = rows + (size_t)(c0 + t) * stride;
+                ml_cp4(qs + t * DP + x, row + q_off + x);
+                ml_cp4(ks + t * DP + x, row + k_off + x);
+            }
         }
         for (int i = tid; i < n * CPB; i += ML_THREADS) {
             const int t = i / CPB, c = blockIdx.x * CPB + (i - t * CPB);
-            vs[i] = c < dv ? rows[(size_t)(c0 + t) * stride + v_off + c] : 1.f;
+            if (c < dv) ml_cp4(vs + i, rows + (size_t)(c0 + t) * stride + v_off + c);
         }
-        for (int i = tid; i < n * 2; i += ML_THREADS) {
-            const int t = i >> 1;
-            gs[i] = gate[((size_t)(c0 + t) * H + h) * 4 + (i & 1)];
-        }
-        __syncthreads();
-        for (int t = 0; t < n; ++t) {
-            const float a = gs[2 * t], bv = gs[2 * t + 1] * vs[t * CPB + cl];
-            const float* kq = ks + t * DP + r0;
-            const float* qq = qs + t * DP + r0;
-            float acc = 0.f;
+        for (int t = tid; t < n; t += ML_THREADS)
+            ml_cp8(gs + 2 * t, gate + ((size_t)(c0 + t) * H + h) * 4);
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+    // a ring of nb buffers: nb - 1 chunks are on their way while one is worked on (a chunk's
+    // arithmetic is shorter than a trip to memory); a group is committed for every chunk, also an
+    // empty one past the end, so that "all but the newest nb - 1" always names this chunk
+    for (int i = 0; i < nb - 1; ++i) {
+        if (a0 + i * ML_TC < a1) request(a0 + i * ML_TC, sm + i * stage);
+        else asm volatile("cp.async.commit_group;\n" ::);
+    }
+    int which = 0;
+    for (int c0 = a0; c0 < a1; c0 += ML_TC, which = which + 1 == nb ? 0 : which + 1) {
+        const int n = min(ML_TC, a1 - c0);
+        const int ahead = c0 + (nb - 1) * ML_TC;
+        if (ahead < a1) request(ahead, sm + (which == 0 ? nb - 1 : which - 1) * stage);
+        else asm volatile("cp.async.commit_group;\n" ::);
+        if (nb == 4) asm volatile("cp.async.wait_group 3;\n" ::);
+        else if (nb == 3) asm volatile("cp.async.wait_group 2;\n" ::);
+        else asm volatile("cp.async.wait_group 1;\n" ::);
+        __syncthreads();                         // this chunk has landed for every thread
+        const float* qs = sm + which * stage;
+        const float* ks = qs + ML_TC * DP;
+        const float* vs = ks + ML_TC * DP;
+        const float* gs = vs + ML_TC * CPB;
+        if (n == ML_TC) {
+            float acc[ML_TC];
 #pragma unroll
-            for (int j = 0; j < R; ++j) {
-                S[j] = fmaf(a, S[j], bv * kq[j]);
-                acc = fmaf(S[j], qq[j], acc);
+            for (int t = 0; t < ML_TC; ++t) {
+                const float a = gs[2 * t], bv = gs[2 * t + 1] * vs[t * CPB + cl];
+                const float4* kq = (const float4*)(ks + t * DP + r0);
+                const float4* qq = (const float4*)(qs + t * DP + r0);
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < R / 4; ++j) {
+                    const float4 k4 = kq[j], q4 = qq[j];
+                    S[4 * j] = fmaf(a, S[4 * j], bv * k4.x);
+                    S[4 * j + 1] = fmaf(a, S[4 * j + 1], bv * k4.y);
+                    S[4 * j + 2] = fmaf(a, S[4 * j + 2], bv * k4.z);
+                    S[4 * j + 3] = fmaf(a, S[4 * j + 3], bv * k4.w);
+                    sum = fmaf(S[4 * j], q4.x, sum);
+                    sum = fmaf(S[4 * j + 1], q4.y, sum);
+                    sum = fmaf(S[4 * j + 2], q4.z, sum);
+                    sum = fmaf(S[4 * j + 3], q4.w, sum);
+                }
+                acc[t] = sum;
             }
-            for (int o = P >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (part == 0 && live) num[((size_t)(c0 + t) * H + h) * W + col] = acc;
+            for (int o = P >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                for (int t = 0; t < ML_TC; ++t) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+            }
+            if (live) {
+#pragma unroll
+                for (int t = 0; t < ML_TC; ++t)
+                    if ((t & (P - 1)) == part)
+                        num[((size_t)(c0 + t) * H + h) * W + col] = acc[t] * q_scale;
+            }
+        } else {
+            for (int t = 0; t < n; ++t) {
+                const float a = gs[2 * t], bv = gs[2 * t + 1] * vs[t * CPB + cl];
+                const float* kq = ks + t * DP + r0;
+                const float* qq = qs + t * DP + r0;
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < R; ++j) {
+                    S[j] = fmaf(a, S[j], bv * kq[j]);
+                    sum = fmaf(S[j], qq[j], sum);
+                }
+                for (int o = P >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                if (part == 0 && live) num[((size_t)(c0 + t) * H + h) * W + col] = sum * q_scale;
+            }
         }
+        __syncthreads();                         // done with this buffer before it is asked for again
     }
     if (live) {
 #pragma unroll
@@ -220,7 +375,13 @@ extern "C" int rv_mlstm(const float* rows, int stride, const float* bi, const fl
     while (P * R < d) P <<= 1;
     const int CPB = ML_THREADS / P;
     const dim3 grid((dv + 1 + CPB - 1) / CPB, H, n_reqs);
-    const size_t smem = (size_t)(2 * ML_TC * P * R + ML_TC * CPB + 2 * ML_TC) * sizeof(float);
+    const size_t stage_bytes = (size_t)(2 * ML_TC * P * R + ML_TC * CPB + 2 * ML_TC) * sizeof(float);
+    const int nb = stage_bytes * 4 <= 64 * 1024 ? 4 : stage_bytes * 3 <= 128 * 1024 ? 3 : 2;
+    const size_t smem = nb * stage_bytes;
+    // 16-byte copies of q and k: every row and every head's stretch begins on a 16-byte boundary
+    // (bit 0); and of a single token's rows of the state as well (bit 1)
+    int vec = d % 4 == 0 && stride % 4 == 0 && ((uintptr_t)rows & 15) == 0;
+    if (vec && rec % 4 == 0 && ((uintptr_t)state & 15) == 0) vec |= 2;
     const float q_scale = 1.f / sqrtf((float)d);
 #define ML_SCAN(RR)                                                                               \
     {                                                                                             \
@@ -230,7 +391,7 @@ extern "C" int rv_mlstm(const float* rows, int stride, const float* bi, const fl
                                  (int)smem) != cudaSuccess)                                       \
             RV_FAIL("mlstm: %zu bytes of shared memory are not to be had", smem);                 \
         rv_launch(mlstm_scan_kernel<RR>, grid, dim3(ML_THREADS), smem, s, rows, stride, H, d, dv, \
-                  P, q_start, state_slot, state, rec, (const float*)gate, num, q_scale);          \
+                  P, q_start, state_slot, state, rec, (const float*)gate, num, q_scale, vec, nb); \
     }
     if (R == 4) ML_SCAN(4)
     else if (R == 8) ML_SCAN(8)
