@@ -151,9 +151,9 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
         const float* kr = row + H * d + h * d;
         const float* qr = row + h * d;
         float sum = 0.f;
-        if (vec & 2) {
+        if (R >= 4 && (vec & 2)) {
 #pragma unroll
-            for (int j = 0; j < R; j += 4) {
+            for (int j = 0; j + 3 < R; j += 4) {
                 if (live && r0 + j < d) {
                     float4 s4 = *(const float4*)(cr + r0 + j);
                     const float4 k4 = *(const float4*)(kr + r0 + j), q4 = *(const float4*)(qr + r0 + j);
@@ -182,13 +182,15 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
         if (part == 0 && live) num[((size_t)a0 * H + h) * (dv + 1) + col] = sum * q_scale;
         return;
     }
-    // zeros where no copy ever writes (rows beyond d, columns beyond dv); ones as the values of
-    // the column of n
+    // A buffer: q [16][DP], k [16][DP], v [CPB][16], a [16], b [16].  Zeros where no copy ever
+    // writes (rows beyond d, columns beyond dv); ones as the values of the column of n.
+    const int sh_cpb = __ffs(CPB) - 1;           // CPB = 128 / P is a power of two
     for (int i = tid; i < nb * stage; i += ML_THREADS) {
         const int x = i % stage - 2 * ML_TC * DP;
-        const bool n_col = x >= 0 && x < ML_TC * CPB && blockIdx.x * CPB + x % CPB == dv;
+        const bool n_col = x >= 0 && x < ML_TC * CPB && blockIdx.x * CPB + (x >> 4) == dv;
         sm[i] = n_col ? 1.f : 0.f;
     }
+    float* psum = sm + nb * stage;               // [16][128]: every lane's part of a column's sum
     rv_pdl_wait();
     float S[R];
     float* col_rec = state + (size_t)slot * rec + ((size_t)h * (dv + 1) + col) * d;
@@ -196,35 +198,43 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
     for (int j = 0; j < R; ++j) S[j] = (live && r0 + j < d) ? col_rec[r0 + j] : 0.f;
     const int q_off = h * d, k_off = H * d + h * d, v_off = 2 * H * d + h * dv;
     const int W = dv + 1;
+    // this thread's first copy of q and k in a chunk (the same in every chunk): token and place
+    const int per_row = (vec & 1) ? (d >> 2) : d;
+    const int t_first = tid / per_row, x_first = tid - t_first * per_row;
+    const int t_step = ML_THREADS / per_row, x_step = ML_THREADS - t_step * per_row;
+    const int v_c = tid & (CPB - 1), v_t = tid >> sh_cpb;
+    const bool v_real = blockIdx.x * CPB + v_c < dv;
     __syncthreads();                             // the buffers are set before any copy lands
     auto request = [&](int c0, float* buf) {
         const int n = min(ML_TC, a1 - c0);
         float* qs = buf;
         float* ks = buf + ML_TC * DP;
         float* vs = ks + ML_TC * DP;
-        float* gs = vs + ML_TC * CPB;
-        if (vec & 1) {
-            const int d4 = d >> 2;
-            for (int i = tid; i < n * d4; i += ML_THREADS) {
-                const int t = i / d4, x = (i - t * d4) << 2;
-                const float* row = rows + (size_t)(c0 + t) * stride;
-                ml_cp16(qs + t * DP + x, row + q_off + x);
-                ml_cp16(ks + t * DP + x, row + k_off + x);
-            }
-        } else {
-            for (int i = tid; i < n * d; i += ML_THREADS) {
-                const int t = i / d, x = i - t * d;
-                const float* row = rows + (size_t)(c0 + t) * stride;
+        float* gab = vs + ML_TC * CPB;
+        int t = t_first, x = x_first;
+        while (t < n) {
+            const float* row = rows + (size_t)(c0 + t) * stride;
+            if (vec & 1) {
+                ml_cp16(qs + t * DP + 4 * x, row + q_off + 4 * x);
+                ml_cp16(ks + t * DP + 4 * x, row + k_off + 4 * x);
+            } else {
                 ml_cp4(qs + t * DP + x, row + q_off + x);
                 ml_cp4(ks + t * DP + x, row + k_off + x);
             }
+            x += x_step;
+            t += t_step;
+            if (x >= per_row) {
+                x -= per_row;
+                ++t;
+            }
         }
-        for (int i = tid; i < n * CPB; i += ML_THREADS) {
-            const int t = i / CPB, c = blockIdx.x * CPB + (i - t * CPB);
-            if (c < dv) ml_cp4(vs + i, rows + (size_t)(c0 + t) * stride + v_off + c);
-        }
-        for (int t = tid; t < n; t += ML_THREADS)
-            ml_cp8(gs + 2 * t, gate + ((size_t)(c0 + t) * H + h) * 4);
+        if (v_real)
+            for (int tv = v_t; tv < n; tv += P)
+                ml_cp4(vs + v_c * ML_TC + tv,
+                       rows + (size_t)(c0 + tv) * stride + v_off + blockIdx.x * CPB + v_c);
+        if (tid < 2 * n)
+            ml_cp4(gab + (tid & 1) * ML_TC + (tid >> 1),
+                   gate + ((size_t)(c0 + (tid >> 1)) * H + h) * 4 + (tid & 1));
         asm volatile("cp.async.commit_group;\n" ::);
     };
     // a ring of nb buffers: nb - 1 chunks are on their way while one is worked on (a chunk's
@@ -246,13 +256,22 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
         __syncthreads();                         // this chunk has landed for every thread
         const float* qs = sm + which * stage;
         const float* ks = qs + ML_TC * DP;
-        const float* vs = ks + ML_TC * DP;
-        const float* gs = vs + ML_TC * CPB;
+        const float* vs = ks + ML_TC * DP + cl * ML_TC;       // this lane's column
+        const float* ga = ks + ML_TC * DP + ML_TC * CPB;
+        const float* gb = ga + ML_TC;
         if (n == ML_TC) {
-            float acc[ML_TC];
+            float a_[ML_TC], bv_[ML_TC];
+#pragma unroll
+            for (int g = 0; g < ML_TC / 4; ++g) {
+                const float4 A = ((const float4*)ga)[g], B = ((const float4*)gb)[g],
+                             V = ((const float4*)vs)[g];
+                a_[4 * g] = A.x; a_[4 * g + 1] = A.y; a_[4 * g + 2] = A.z; a_[4 * g + 3] = A.w;
+                bv_[4 * g] = B.x * V.x; bv_[4 * g + 1] = B.y * V.y;
+                bv_[4 * g + 2] = B.z * V.z; bv_[4 * g + 3] = B.w * V.w;
+            }
 #pragma unroll
             for (int t = 0; t < ML_TC; ++t) {
-                const float a = gs[2 * t], bv = gs[2 * t + 1] * vs[t * CPB + cl];
+                const float a = a_[t], bv = bv_[t];
                 const float4* kq = (const float4*)(ks + t * DP + r0);
                 const float4* qq = (const float4*)(qs + t * DP + r0);
                 float sum = 0.f;
@@ -268,21 +287,23 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
                     sum = fmaf(S[4 * j + 2], q4.z, sum);
                     sum = fmaf(S[4 * j + 3], q4.w, sum);
                 }
-                acc[t] = sum;
+                psum[t * ML_THREADS + tid] = sum;
             }
-            for (int o = P >> 1; o > 0; o >>= 1) {
-#pragma unroll
-                for (int t = 0; t < ML_TC; ++t) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
-            }
-            if (live) {
-#pragma unroll
-                for (int t = 0; t < ML_TC; ++t)
-                    if ((t & (P - 1)) == part)
-                        num[((size_t)(c0 + t) * H + h) * W + col] = acc[t] * q_scale;
+            __syncthreads();
+            // a thread adds the P parts of one (token, column) in the lanes' order and writes it
+            for (int o = tid; o < ML_TC * CPB; o += ML_THREADS) {
+                const int t = o >> sh_cpb, c = o & (CPB - 1);
+                const int colg = blockIdx.x * CPB + c;
+                if (colg <= dv) {
+                    const float* pp = psum + t * ML_THREADS + c * P;
+                    float sum = 0.f;
+                    for (int i = 0; i < P; ++i) sum += pp[i];
+                    num[((size_t)(c0 + t) * H + h) * W + colg] = sum * q_scale;
+                }
             }
         } else {
             for (int t = 0; t < n; ++t) {
-                const float a = gs[2 * t], bv = gs[2 * t + 1] * vs[t * CPB + cl];
+                const float a = ga[t], bv = gb[t] * vs[t];
                 const float* kq = ks + t * DP + r0;
                 const float* qq = qs + t * DP + r0;
                 float sum = 0.f;
@@ -348,6 +369,9 @@ extern "C" long long rv_mlstm_scratch(int n_tokens, int H, int dv) {
     return (long long)n_tokens * H * (4 + dv + 1);
 }
 
+// Rows of a column a lane holds.  (Two rows a lane, which doubles the warps of a single prompt,
+// measured slower at key size 64: 437 against 274 us for 2,048 tokens of 8 heads; what a block
+// does per chunk besides its multiply-adds is what costs.)
 static int ml_rows_per_lane(int d) { return d <= 64 ? 4 : d <= 256 ? 8 : 16; }
 
 extern "C" int rv_mlstm(const float* rows, int stride, const float* bi, const float* bf,
@@ -376,8 +400,8 @@ extern "C" int rv_mlstm(const float* rows, int stride, const float* bi, const fl
     const int CPB = ML_THREADS / P;
     const dim3 grid((dv + 1 + CPB - 1) / CPB, H, n_reqs);
     const size_t stage_bytes = (size_t)(2 * ML_TC * P * R + ML_TC * CPB + 2 * ML_TC) * sizeof(float);
-    const int nb = stage_bytes * 4 <= 64 * 1024 ? 4 : stage_bytes * 3 <= 128 * 1024 ? 3 : 2;
-    const size_t smem = nb * stage_bytes;
+    const int nb = stage_bytes * 4 <= 64 * 1024 ? 4 : stage_bytes * 3 <= 128 * 1024 ? 3 : 2;   // ring
+    const size_t smem = nb * stage_bytes + (size_t)ML_TC * ML_THREADS * sizeof(float);
     // 16-byte copies of q and k: every row and every head's stretch begins on a 16-byte boundary
     // (bit 0); and of a single token's rows of the state as well (bit 1)
     int vec = d % 4 == 0 && stride % 4 == 0 && ((uintptr_t)rows & 15) == 0;
