@@ -957,7 +957,7 @@ def mevuvik_config(sz):
         layers.append({"type": "latent_attention", "mixer": latent, "mlp": mlp} if i % 2 == 0 else
                       {"type": "parallel", "mixer": par, "mlp": mlp})
     return {"architecture": "Mevuvik", "vocab": sz["vocab"], "width": sz["width"],
-            "norm": {"eps": 1e-5}, "residual_mult": 0.5, "logit_softcap": 30.0,
+            "norm": {"eps": 1e-5}, "residual_mult": 0.7, "logit_softcap": 25.0,
             "loop": {"start": 2, "stop": 4, "times": 2}, "layers": layers}
 
 

@@ -71,11 +71,11 @@ MV_B = {
 # width of 50; the repeated stretch is the whole model, run twice
 MV_C = {
     "architecture": "Mevuvik", "vocab": 99, "width": 50, "norm": {"eps": 1e-5},
-    "residual_mult": 0.5, "logit_softcap": 30.0, "loop": {"start": 0, "stop": 2, "times": 2},
+    "residual_mult": 0.4, "logit_softcap": 25.0, "loop": {"start": 0, "stop": 2, "times": 2},
     "layers": [
-        {"type": "latent_attention", "mixer": _latent(3, 10, 6, 6, 14, 9, 0.3, 1e6),
-         "mlp": _moe(34, 3, 2, 2.0)},
-        {"type": "parallel", "mixer": _parallel((3, 3, 10, 6, 0.6), (2, 6, 5, 12.0), 1.2, 0.9),
+        {"type": "latent_attention", "mixer": _latent(3, 10, 6, 6, 14, 9, 0.3, 2e5),
+         "mlp": _moe(34, 3, 2, 1.8)},
+        {"type": "parallel", "mixer": _parallel((3, 3, 10, 6, 0.6), (2, 6, 5, 7.0), 1.4, 0.75),
          "mlp": _dense(22)},
     ],
 }
@@ -83,13 +83,13 @@ MV_C = {
 # sizes the tensor-core kernels take in bfloat16; a stretch that runs once
 MV_D = {
     "architecture": "Mevuvik", "vocab": 200, "width": 128, "norm": {"eps": 1e-6},
-    "residual_mult": 0.5, "logit_softcap": 20.0, "loop": {"start": 2, "stop": 3, "times": 1},
+    "residual_mult": 0.6, "logit_softcap": 20.0, "loop": {"start": 2, "stop": 3, "times": 1},
     "layers": [
         {"type": "latent_attention", "mixer": _latent(8, 32, 16, 48, 48, 64, 0.18, 1e4),
          "mlp": _moe(64, 16, 4, 2.0)},
-        {"type": "parallel", "mixer": _parallel((8, 2, 64, 64, 0.2), (4, 64, 64, 12.0), 1.0, 1.0),
+        {"type": "parallel", "mixer": _parallel((8, 2, 64, 64, 0.2), (4, 64, 64, 11.0), 1.0, 1.0),
          "mlp": _dense(256)},
-        {"type": "latent_attention", "mixer": _latent(4, 64, 32, 32, 96, 32, 0.12, 1e6),
+        {"type": "latent_attention", "mixer": _latent(4, 64, 32, 32, 96, 32, 0.12, 3e5),
          "mlp": _moe(128, 4, 2, 1.0)},
         {"type": "parallel", "mixer": _parallel((4, 4, 32, 32, 0.3), (2, 128, 32, 10.0), 0.7, 1.4),
          "mlp": None},
