@@ -190,7 +190,11 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
         const bool n_col = x >= 0 && x < ML_TC * CPB && blockIdx.x * CPB + (x >> 4) == dv;
         sm[i] = n_col ? 1.f : 0.f;
     }
-    float* psum = sm + nb * stage;               // [16][128]: every lane's part of a column's sum
+    // every lane's part of a column's sum: [16][CPB][P + 1].  A column's P parts lie side by
+    // side; the one float between columns keeps the lanes that write and the threads that add
+    // them on different banks.
+    float* psum = sm + nb * stage;
+    const int pitch = ML_THREADS + CPB;
     rv_pdl_wait();
     float S[R];
     float* col_rec = state + (size_t)slot * rec + ((size_t)h * (dv + 1) + col) * d;
@@ -287,7 +291,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
                     sum = fmaf(S[4 * j + 2], q4.z, sum);
                     sum = fmaf(S[4 * j + 3], q4.w, sum);
                 }
-                psum[t * ML_THREADS + tid] = sum;
+                psum[t * pitch + cl * (P + 1) + part] = sum;
             }
             __syncthreads();
             // a thread adds the P parts of one (token, column) in the lanes' order and writes it
@@ -295,7 +299,7 @@ __global__ void __launch_bounds__(ML_THREADS) mlstm_scan_kernel(
                 const int t = o >> sh_cpb, c = o & (CPB - 1);
                 const int colg = blockIdx.x * CPB + c;
                 if (colg <= dv) {
-                    const float* pp = psum + t * ML_THREADS + c * P;
+                    const float* pp = psum + t * pitch + c * (P + 1);
                     float sum = 0.f;
                     for (int i = 0; i < P; ++i) sum += pp[i];
                     num[((size_t)(c0 + t) * H + h) * W + colg] = sum * q_scale;
@@ -401,7 +405,7 @@ extern "C" int rv_mlstm(const float* rows, int stride, const float* bi, const fl
     const dim3 grid((dv + 1 + CPB - 1) / CPB, H, n_reqs);
     const size_t stage_bytes = (size_t)(2 * ML_TC * P * R + ML_TC * CPB + 2 * ML_TC) * sizeof(float);
     const int nb = stage_bytes * 4 <= 64 * 1024 ? 4 : stage_bytes * 3 <= 128 * 1024 ? 3 : 2;   // ring
-    const size_t smem = nb * stage_bytes + (size_t)ML_TC * ML_THREADS * sizeof(float);
+    const size_t smem = nb * stage_bytes + (size_t)ML_TC * (ML_THREADS + CPB) * sizeof(float);
     // 16-byte copies of q and k: every row and every head's stretch begins on a 16-byte boundary
     // (bit 0); and of a single token's rows of the state as well (bit 1)
     int vec = d % 4 == 0 && stride % 4 == 0 && ((uintptr_t)rows & 15) == 0;
