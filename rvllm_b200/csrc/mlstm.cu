@@ -37,7 +37,7 @@ __device__ __forceinline__ float ml_logsigmoid(float z) {
     return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
-__global__ void __launch_bounds__(ML_THREADS) mlstm_gates_kernel(
+__global__ void __launch_bounds__(512) mlstm_gates_kernel(
     const float* __restrict__ rows, int stride, int i_off, int f_off, const float* __restrict__ bi,
     const float* __restrict__ bf, float cap, const int* __restrict__ q_start,
     const int* __restrict__ state_slot, float* __restrict__ state, long long rec, int m_off,
@@ -395,7 +395,9 @@ extern "C" int rv_mlstm(const float* rows, int stride, const float* bi, const fl
     const int i_off = 2 * H * d + H * dv, f_off = i_off + H, g_off = f_off + H;
     float* gate = scratch;
     float* num = scratch + (size_t)n_tokens * H * 4;
-    rv_launch(mlstm_gates_kernel, dim3(n_reqs, H), dim3(ML_THREADS), 0, s, rows, stride, i_off, f_off,
+    // the gates of a long portion are formed by many threads; the chain between them is one thread's
+    const int gate_threads = n_tokens / n_reqs >= 256 ? 512 : ML_THREADS;
+    rv_launch(mlstm_gates_kernel, dim3(n_reqs, H), dim3(gate_threads), 0, s, rows, stride, i_off, f_off,
               bi, bf, cap, q_start, state_slot, state, rec, H * (dv + 1) * d, gate, H);
     RV_CHECK_LAUNCH("mlstm_gates");
     const int R = ml_rows_per_lane(d);
